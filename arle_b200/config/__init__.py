@@ -1,5 +1,6 @@
 from .model_spec import ModelSpec, ScheduleEntry
 from .kolodra import KolodraConfig
+from .lasupel import LasupelConfig
 from .qwen3 import ConfigError, Qwen3Config
 from .zuderax import ZuderaxConfig
 from .registry import (UnknownArchitecture, config_class_for, config_from_dict, load_config,
@@ -8,6 +9,7 @@ from .registry import (UnknownArchitecture, config_class_for, config_from_dict, 
 register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(KolodraConfig.architecture, KolodraConfig)
 register_architecture(ZuderaxConfig.architecture, ZuderaxConfig)
+register_architecture(LasupelConfig.architecture, LasupelConfig)
 
-__all__ = ["ModelSpec", "ScheduleEntry", "ConfigError", "Qwen3Config", "KolodraConfig", "ZuderaxConfig", "UnknownArchitecture", "config_class_for",
+__all__ = ["ModelSpec", "ScheduleEntry", "ConfigError", "Qwen3Config", "KolodraConfig", "ZuderaxConfig", "LasupelConfig", "UnknownArchitecture", "config_class_for",
            "config_from_dict", "load_config", "register_architecture", "registered_architectures"]

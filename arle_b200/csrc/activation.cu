@@ -91,3 +91,38 @@ ARLE_API int arle_act_mul(const void* gu, void* out, int dtype, int num_tokens, 
   return act == 0 ? act_mul_launch<0>(gu, out, dtype, num_tokens, inter, out_stride, s)
                   : act_mul_launch<1>(gu, out, dtype, num_tokens, inter, out_stride, s);
 }
+
+// A gated unit with clamped inputs: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + 1); float32 arithmetic, rounded once.  gate_up [T, 2I] with (gate_i, up_i) in
+// columns 2i and 2i + 1.
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, int out_stride, float limit,
+                                   float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = fminf(to_f32(gu[t * 2 * inter + 2 * i]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[t * 2 * inter + 2 * i + 1]), -limit), limit);
+    out[t * (size_t)out_stride + i] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+  }
+}
+
+ARLE_API int arle_clamped_glu(const void* gu, void* out, int dtype, int num_tokens, int inter, int out_stride, float limit, float alpha,
+                              cudaStream_t s) {
+  if (num_tokens <= 0) return 0;
+  if (inter <= 0 || out_stride < inter || !(limit > 0.f)) return ARLE_E_BADARG;
+  const size_t total = (size_t)num_tokens * inter;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == 0)
+    launch_kernel(clamped_glu_kernel<float>, dim3((int)blocks), dim3(256), 0, s, 1, (const float*)gu, (float*)out, inter, total, out_stride,
+                  limit, alpha);
+  else if (dtype == 1)
+    launch_kernel(clamped_glu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                  inter, total, out_stride, limit, alpha);
+  else
+    return ARLE_E_BADARG;
+  return launch_status();
+}

@@ -10,6 +10,10 @@
 // the four partial results are merged at the end.  The order of all sums depends
 // on (first key, p) only, so a token's result is the same however the prompt was
 // cut into steps and whatever else is in the batch.
+//
+// Values may have another width than keys (vd; the value cache is [page][kv_head][slot][vd]).  With a sink the
+// softmax has one more term in its denominator, exp(sink_logit), that carries no value:
+// p_j = exp(s_j) / (exp(sink_logit) + sum exp(s_j)).
 #include "common.cuh"
 using namespace arle;
 
@@ -22,7 +26,8 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, int q_row_
                                              const int* __restrict__ positions,
                                              const int* __restrict__ row_of_token,
                                              const int* __restrict__ block_table, int bt_stride, int nq,
-                                             int nkv, int hd, int page_size, float scale, int window) {
+                                             int nkv, int hd, int vd, int page_size, float scale, int window, int has_sink,
+                                             float sink_logit) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float qs[256];
@@ -45,6 +50,7 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, int q_row_
   for (int i = 0; i < kAttnMaxD; ++i) acc[i] = 0.f;
 
   const size_t page_stride = (size_t)nkv * page_size * hd;
+  const size_t vpage_stride = (size_t)nkv * page_size * vd;
   for (int j0 = lo + w * 32; j0 <= pos; j0 += kAttnWarps * 32) {
     const int j = j0 + lane;
     float sc = -INFINITY;
@@ -68,11 +74,11 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, int q_row_
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int jk = j0 + jj;
       const int page = bt[jk / page_size];
-      const T* vp = v_cache + (size_t)page * page_stride + ((size_t)kvh * page_size + jk % page_size) * hd;
+      const T* vp = v_cache + (size_t)page * vpage_stride + ((size_t)kvh * page_size + jk % page_size) * vd;
 #pragma unroll
       for (int i = 0; i < kAttnMaxD; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) acc[i] = fmaf(pj, to_f32(vp[d]), acc[i]);
+        if (d < vd) acc[i] = fmaf(pj, to_f32(vp[d]), acc[i]);
       }
     }
   }
@@ -83,18 +89,18 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, int q_row_
 #pragma unroll
   for (int i = 0; i < kAttnMaxD; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) acc_s[w][d] = acc[i];
+    if (d < vd) acc_s[w][d] = acc[i];
   }
   __syncthreads();
-  float mm = m_s[0];
-  for (int i = 1; i < kAttnWarps; ++i) mm = fmaxf(mm, m_s[i]);
-  float f[kAttnWarps], ll = 0.f;
+  float mm = has_sink ? sink_logit : m_s[0];
+  for (int i = has_sink ? 0 : 1; i < kAttnWarps; ++i) mm = fmaxf(mm, m_s[i]);
+  float f[kAttnWarps], ll = has_sink ? expf(sink_logit - mm) : 0.f;
   for (int i = 0; i < kAttnWarps; ++i) {
     f[i] = expf(m_s[i] - mm);  // a warp without keys has m = -inf, so f = 0
     ll += l_s[i] * f[i];
   }
-  T* op = out + ((size_t)t * nq + h) * hd;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+  T* op = out + ((size_t)t * nq + h) * vd;
+  for (int d = threadIdx.x; d < vd; d += blockDim.x) {
     float o = 0.f;
     for (int i = 0; i < kAttnWarps; ++i) o += acc_s[i][d] * f[i];
     op[d] = from_f32<T>(o / ll);
@@ -104,21 +110,22 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, int q_row_
 ARLE_API int arle_paged_attention_plain(const void* q, int q_row_stride, void* out, const void* k_cache,
                                         const void* v_cache, int dtype, const int* positions,
                                         const int* row_of_token, const int* block_table, int bt_stride,
-                                        int nq, int nkv, int hd, int page_size, float scale, int window,
-                                        int num_tokens, cudaStream_t s) {
+                                        int nq, int nkv, int hd, int vd, int page_size, float scale, int window,
+                                        int has_sink, float sink_logit, int num_tokens, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
+  if (vd <= 0 || vd > 256) return ARLE_E_UNSUPPORTED;
   if (hd <= 0 || hd > 256 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0) return ARLE_E_UNSUPPORTED;
   if (nq > 65535) return ARLE_E_UNSUPPORTED;
   dim3 grid(num_tokens, nq);
   if (dtype == 0)
     launch_kernel(paged_attention_plain_kernel<float>, dim3(grid), dim3(kAttnWarps * 32), 0, s, 1, 
         (const float*)q, q_row_stride, (float*)out, (const float*)k_cache, (const float*)v_cache, positions,
-        row_of_token, block_table, bt_stride, nq, nkv, hd, page_size, scale, window);
+        row_of_token, block_table, bt_stride, nq, nkv, hd, vd, page_size, scale, window, has_sink, sink_logit);
   else if (dtype == 1)
     launch_kernel(paged_attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(kAttnWarps * 32), 0, s, 1, 
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
-        (const __nv_bfloat16*)v_cache, positions, row_of_token, block_table, bt_stride, nq, nkv, hd,
-        page_size, scale, window);
+        (const __nv_bfloat16*)v_cache, positions, row_of_token, block_table, bt_stride, nq, nkv, hd, vd,
+        page_size, scale, window, has_sink, sink_logit);
   else
     return ARLE_E_BADARG;
   return launch_status();

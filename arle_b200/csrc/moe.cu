@@ -4,7 +4,8 @@
 //    stand in `groups` equal groups of neighbours, a group's score is the sum of its two largest choice scores (its one
 //    score when a group is a single expert), only experts of the `keep` best groups can be chosen (the others count as
 //    minus infinity); the `top` largest choice scores are chosen and weighted with s * scale (no renormalisation).
-//    Ties go to the lower index.  One thread per token, everything float32.
+//    Ties go to the lower index.  One thread per token, everything float32.  `mode` bit 0: the scores are a softmax
+//    over all experts instead of sigmoids; bit 1: a group's score is its largest choice score alone.
 //  * moe_plan: sorts the step's (token, choice) pairs by expert (counts, offsets, a place for every pair) and lists
 //    the tiles of 64 places that the grouped product runs, one block of 1,024 threads; nothing goes through the host,
 //    so the step can be captured in a graph.  The order of the pairs inside an expert's run is whatever the
@@ -23,7 +24,7 @@ using namespace arle;
 
 __global__ void moe_select_kernel(const float* __restrict__ z, int z_stride, const float* __restrict__ correction,
                                   float* __restrict__ scratch, int E, int top, int groups, int keep, float scale,
-                                  int* __restrict__ ids, float* __restrict__ wts, int num_tokens) {
+                                  int mode, int* __restrict__ ids, float* __restrict__ wts, int num_tokens) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -31,7 +32,14 @@ __global__ void moe_select_kernel(const float* __restrict__ z, int z_stride, con
   const float* zr = z + (size_t)t * z_stride;
   float* ch = scratch + (size_t)t * (E + groups);       // choice scores, then the groups' scores
   float* gs = ch + E;
-  for (int e = 0; e < E; ++e) ch[e] = 1.0f / (1.0f + expf(-zr[e])) + (correction ? correction[e] : 0.f);
+  float zmax = -INFINITY, zsum = 1.f;
+  if (mode & 1) {
+    for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, zr[e]);
+    zsum = 0.f;
+    for (int e = 0; e < E; ++e) zsum += expf(zr[e] - zmax);
+  }
+  for (int e = 0; e < E; ++e)
+    ch[e] = ((mode & 1) ? expf(zr[e] - zmax) / zsum : 1.0f / (1.0f + expf(-zr[e]))) + (correction ? correction[e] : 0.f);
   const int per = E / groups;
   for (int g = 0; g < groups; ++g) {
     float b1 = -INFINITY, b2 = -INFINITY;
@@ -44,7 +52,7 @@ __global__ void moe_select_kernel(const float* __restrict__ z, int z_stride, con
         b2 = v;
       }
     }
-    gs[g] = per > 1 ? b1 + b2 : b1;
+    gs[g] = (per > 1 && !(mode & 2)) ? b1 + b2 : b1;
   }
   if (keep < groups) {
     // the groups that are not kept: all but the `keep` best
@@ -76,16 +84,16 @@ __global__ void moe_select_kernel(const float* __restrict__ z, int z_stride, con
     }
     ch[bi] = INFINITY;                                  // taken
     ids[(size_t)t * top + it] = bi;
-    wts[(size_t)t * top + it] = scale / (1.0f + expf(-zr[bi]));
+    wts[(size_t)t * top + it] = (mode & 1) ? scale * (expf(zr[bi] - zmax) / zsum) : scale / (1.0f + expf(-zr[bi]));
   }
 }
 
 ARLE_API int arle_moe_select(const float* z, int z_stride, const float* correction, float* scratch, int E, int top, int groups,
-                             int keep, float scale, int* ids, float* wts, int num_tokens, cudaStream_t s) {
+                             int keep, float scale, int mode, int* ids, float* wts, int num_tokens, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
   if (E <= 0 || top <= 0 || groups <= 0 || E % groups || keep <= 0 || keep > groups || top > keep * (E / groups)) return ARLE_E_BADARG;
   launch_kernel(moe_select_kernel, dim3((num_tokens + 63) / 64), dim3(64), 0, s, 1, z, z_stride, correction, scratch, E, top, groups,
-                keep, scale, ids, wts, num_tokens);
+                keep, scale, mode, ids, wts, num_tokens);
   return launch_status();
 }
 

@@ -53,7 +53,14 @@ _SIGNATURES = {
     "arle_gla_out": [_P, _P, _I, _I, _P, _F, _F, _P, _I, _I, _I, _I, _P],
     "arle_attention_prep": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_rotary_angles": [_P, _P, _P, _I, _I, _P],
-    "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _F, _I, _P],
+    "arle_attention_prep_post": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "arle_branch_norm_add": [_P, _P, _I, _P, _P, _I, _I, _I, _F, _P],
+    "arle_causal_conv": [_P, _I, _I, _P, _P, _P, _I, _P, ctypes.c_long, ctypes.c_long, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "arle_rglru_scan": [_P, _P, _P, _I, _I, _P, _P, _P, _P, _F, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "arle_delta_gates": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
+    "arle_delta_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
+    "arle_clamped_glu": [_P, _P, _I, _I, _I, _I, _F, _F, _P],
     "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_paged_attention_decode_stream": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
                                            _F, _I, _I, _I, _P, _P],
@@ -86,7 +93,7 @@ _SIGNATURES = {
     "arle_ssm_gates": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
     "arle_conv_silu": [_P, _I, _I, _P, _P, _P, ctypes.c_long, ctypes.c_long, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_gated_group_norm": [_P, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _I, _P],
-    "arle_moe_select": [_P, _I, _P, _P, _I, _I, _I, _I, _F, _P, _P, _I, _P],
+    "arle_moe_select": [_P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P, _I, _P],
     "arle_moe_plan": [_P, _I, _I, _I, _P, _P, _P, _P],
     "arle_moe_gemm": [_P, _I, _P, _P, _I, ctypes.c_long, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P],
     "arle_moe_combine": [_P, _I, _P, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
@@ -514,8 +521,12 @@ def attention_prep(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_fr
 
 
 def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_table, nq: int, nkv: int, hd: int,
-                    page_size: int, scale: float, window, batch=None) -> None:
+                    page_size: int, scale: float, window, batch=None, vd: int = None, sink: float = None) -> None:
     """Causal attention of this step's queries over the paged cache.
+
+    ``vd``: the values' width when it differs from the keys' (the value cache is then [pages, nkv, page_size, vd] and
+    out [T, nq*vd]).  ``sink``: the score of a sink without a value that the softmax's denominator counts besides the
+    keys, p_j = exp(s_j) / (exp(sink) + sum exp(s_j)); None for the usual softmax.  Both run on the general kernel.
 
     q: [T, nq*hd] view (row stride free, unit inner stride); out: contiguous
     [T, nq*hd]; caches [pages, nkv, page_size, hd]; positions / row_of_token int32
@@ -523,18 +534,21 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
     keys.  ``batch`` (a StepContext) lets faster kernels pick their launch shape;
     the general kernel does not need it."""
     T = q.shape[0]
-    if q.stride(1) != 1 or q.shape[1] != nq * hd or out.shape != (T, nq * hd) or not out.is_contiguous():
-        raise KernelError("paged_attention: q must be [T, nq*hd] with unit inner stride and out contiguous [T, nq*hd]")
+    vd = hd if vd is None else int(vd)
+    if q.stride(1) != 1 or q.shape[1] != nq * hd or out.shape != (T, nq * vd) or not out.is_contiguous():
+        raise KernelError("paged_attention: q must be [T, nq*hd] with unit inner stride and out contiguous [T, nq*vd]")
     if q.dtype != k_cache.dtype or out.dtype != q.dtype:
         raise KernelError("paged_attention: q, out and cache must share a type")
-    if hd > 256 or nq % nkv:
-        raise KernelError(f"paged_attention: head_dim {hd} / heads {nq}:{nkv} not supported")
-    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or not k_cache.is_contiguous() or not v_cache.is_contiguous():
-        raise KernelError(f"paged_attention: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
+    if hd > 256 or vd > 256 or nq % nkv:
+        raise KernelError(f"paged_attention: head_dim {hd} / value width {vd} / heads {nq}:{nkv} not supported")
+    if (tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or tuple(v_cache.shape[1:]) != (nkv, page_size, vd)
+            or not k_cache.is_contiguous() or not v_cache.is_contiguous()):
+        raise KernelError(f"paged_attention: cache shapes {tuple(k_cache.shape)}, {tuple(v_cache.shape)} are not "
+                          f"[pages, {nkv}, {page_size}, {hd}] and [pages, {nkv}, {page_size}, {vd}]")
     _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _i32(block_table, "block_table")
     if block_table.stride(1) != 1:
         raise KernelError("paged_attention: block table rows must be contiguous")
-    if batch is not None and _KERNEL_SET == "fast" and fast_attention_supported(q, nq, nkv, hd):
+    if batch is not None and _KERNEL_SET == "fast" and vd == hd and sink is None and fast_attention_supported(q, nq, nkv, hd):
         if batch.max_q_len > 1:
             prefill = paged_attention_prefill_tc if tc_attention_supported(q, hd, page_size) else paged_attention_prefill
             prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
@@ -559,8 +573,8 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
         return
     _check(library().arle_paged_attention_plain(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _dt(q), _ptr(positions), _ptr(row_of_token),
-        _ptr(block_table), block_table.stride(0), nq, nkv, hd, page_size, float(scale),
-        int(window) if window else 0, T, _stream()), "paged_attention")
+        _ptr(block_table), block_table.stride(0), nq, nkv, hd, vd, page_size, float(scale),
+        int(window) if window else 0, int(sink is not None), float(sink or 0.0), T, _stream()), "paged_attention")
 
 
 def fast_attention_supported(q, nq: int, nkv: int, hd: int) -> bool:
@@ -1266,12 +1280,17 @@ def gated_group_norm(y, x, skip, vdim: int, z, weight, eps: float, out, parts: i
 
 
 # ------------------------------------------------------------------ routed experts
-def moe_select(z, correction, scratch, experts: int, top: int, groups: int, keep: int, scale: float, ids, weights) -> None:
+def moe_select(z, correction, scratch, experts: int, top: int, groups: int, keep: int, scale: float, ids, weights,
+               scores: str = "sigmoid", group_score: str = "top2_sum") -> None:
     """Chooses ``top`` experts per token from float32 router sums z [T, >= experts] (any row stride): scores sigmoid(z),
     choice scores with ``correction`` (float32 [experts] or None) added, experts in ``groups`` equal groups of neighbours of
     which only the ``keep`` with the best scores (sum of a group's two largest choice scores) can be chosen; ids int32
-    [T, top] in the order chosen, weights float32 [T, top] = sigmoid(z) * scale.  scratch float32 [T, experts + groups]."""
+    [T, top] in the order chosen, weights float32 [T, top] = sigmoid(z) * scale.  scratch float32 [T, experts + groups].
+    ``scores`` "softmax": the scores are softmax(z) over all experts; ``group_score`` "max": a group's score is its largest
+    choice score alone."""
     T = z.shape[0]
+    if scores not in ("sigmoid", "softmax") or group_score not in ("top2_sum", "max"):
+        raise KernelError(f"moe_select: scores {scores!r} / group_score {group_score!r} not known")
     if z.dtype != torch.float32 or z.stride(1) != 1 or z.shape[1] < experts:
         raise KernelError("moe_select: z must be float32 [T, >= experts] with unit inner stride")
     if correction is not None and (correction.dtype != torch.float32 or correction.numel() != experts):
@@ -1282,7 +1301,8 @@ def moe_select(z, correction, scratch, experts: int, top: int, groups: int, keep
             or not ids.is_contiguous() or not weights.is_contiguous()):
         raise KernelError("moe_select: ids int32 [T, top] and weights float32 [T, top], contiguous")
     _check(library().arle_moe_select(_ptr(z), z.stride(0), _ptr(correction), _ptr(scratch), experts, top, groups, keep, float(scale),
-                                     _ptr(ids), _ptr(weights), T, _stream()), "moe_select")
+                                     int(scores == "softmax") | (int(group_score == "max") << 1), _ptr(ids), _ptr(weights), T,
+                                     _stream()), "moe_select")
 
 
 def moe_plan_size(experts: int, pairs: int) -> int:
@@ -1339,3 +1359,164 @@ def moe_combine(y, place_of_pair, weights, shared, gate, out) -> None:
     _check(library().arle_moe_combine(_ptr(y), y.stride(0), _ptr(place_of_pair), _ptr(weights), top, _ptr(shared),
                                       shared.stride(0) if shared is not None else 0, _ptr(gate), gate.stride(0) if gate is not None else 0,
                                       _ptr(out), out.stride(0), _dt(out), T, width, _stream()), "moe_combine")
+
+
+# ------------------------------------------------------------------ parts of further designs
+def clamped_glu(gate_up, out, limit: float, alpha: float) -> None:
+    """out[t, i] = g * sigmoid(alpha * g) * (u + 1) with g = min(gate_up[t, 2i], limit) and u = gate_up[t, 2i + 1] clamped to
+    [-limit, limit]; float32 arithmetic, rounded once.  ``out`` may be columns of a wider buffer."""
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or out.stride(1) != 1 or gate_up.dtype != out.dtype:
+        raise KernelError("clamped_glu: gate_up must be contiguous [T, 2I] and out [T, I] of the same type with unit inner stride")
+    _check(library().arle_clamped_glu(_ptr(gate_up), _ptr(out), _dt(out), T, I, out.stride(0) if T > 1 else I, float(limit),
+                                      float(alpha), _stream()), "clamped_glu")
+
+
+def branch_norm_add(resid, branch, weight, eps: float, copy) -> None:
+    """resid += branch / sqrt(mean(branch^2) + eps) * weight per row, in float32; ``copy`` (or None) gets the new residual
+    in its own type.  ``branch`` None: only the copy is written.  resid float32 [T, H] contiguous; branch [T, H] (unit inner
+    stride) and copy [T, H] contiguous in the activation type; weight float32 [H]."""
+    T, H = resid.shape
+    if resid.dtype != torch.float32 or not resid.is_contiguous():
+        raise KernelError("branch_norm_add: the residual must be contiguous float32")
+    if branch is not None and (tuple(branch.shape) != (T, H) or branch.stride(1) != 1 or weight is None
+                               or weight.dtype != torch.float32 or weight.numel() != H):
+        raise KernelError("branch_norm_add: branch [T, H] with unit inner stride and weight float32 [H]")
+    if copy is not None and (tuple(copy.shape) != (T, H) or not copy.is_contiguous()):
+        raise KernelError("branch_norm_add: copy must be contiguous [T, H]")
+    if branch is not None and copy is not None and branch.dtype != copy.dtype:
+        raise KernelError("branch_norm_add: branch and copy must share a type")
+    if branch is None and copy is None:
+        return
+    _check(library().arle_branch_norm_add(_ptr(resid), _ptr(branch), branch.stride(0) if branch is not None else 0, _ptr(weight),
+                                          _ptr(copy), _dt(branch if branch is not None else copy), T, H, float(eps), _stream()),
+           "branch_norm_add")
+
+
+def attention_prep_post(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim: int, k_cache, v_cache,
+                        nq: int, nkv: int, hd: int, vd: int, page_size: int) -> None:
+    """Rotation first, then the per-head norm x / sqrt(mean(x^2) + eps) (times a weight float32 [hd], or none), in place on
+    the q heads of qkv [T, nq*hd + nkv*hd + nkv*vd]; the k heads go the same way into k_cache [pages, nkv, page_size, hd]
+    and the v heads as they are into v_cache [pages, nkv, page_size, vd] (nkv = 0: the rows hold q only and nothing is
+    stored).  ``eps`` None: no norm.  Rotation as in ``attention_prep`` (number i with i + rotary_dim/2)."""
+    T = qkv.shape[0]
+    if qkv.stride(1) != 1 or qkv.shape[1] < nq * hd + nkv * (hd + vd):
+        raise KernelError("attention_prep_post: qkv must be [T, >= nq*hd + nkv*(hd + vd)] with unit inner stride")
+    if hd > 256 or rotary_dim % 2 or rotary_dim > hd:
+        raise KernelError(f"attention_prep_post: head_dim {hd} / rotary_dim {rotary_dim} not supported")
+    for w_ in (q_weight, k_weight):
+        if w_ is not None and (w_.dtype != torch.float32 or w_.numel() != hd):
+            raise KernelError("attention_prep_post: norm weights must be float32 [head_dim]")
+    if nkv > 0:
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise KernelError("attention_prep_post: cache type differs from activation type")
+        if (tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or tuple(v_cache.shape[1:]) != (nkv, page_size, vd)
+                or not k_cache.is_contiguous() or not v_cache.is_contiguous()):
+            raise KernelError(f"attention_prep_post: cache shapes {tuple(k_cache.shape)}, {tuple(v_cache.shape)}")
+        _i32(slot_mapping, "slot_mapping")
+    _i32(positions, "positions")
+    if rotary_dim and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("attention_prep_post: inv_freq must be float32 [rotary_dim / 2]")
+    _check(library().arle_attention_prep_post(
+        _ptr(qkv), _dt(qkv), qkv.stride(0), _ptr(positions), _ptr(slot_mapping) if nkv else None, _ptr(q_weight), _ptr(k_weight),
+        float(eps) if eps is not None else -1.0, _ptr(inv_freq) if rotary_dim else None, int(rotary_dim),
+        _ptr(k_cache) if nkv else None, _ptr(v_cache) if nkv else None, nq, nkv, hd, vd, page_size, T, _stream()),
+        "attention_prep_post")
+
+
+def causal_conv(x, in_bias, weight, out_bias, act: str, state, conv_offset: int, q_indptr, row_of_token, state_slots, out) -> None:
+    """out[t, c] = act(out_bias[c] + sum_j weight[c, j] * in[t - (taps - 1) + j, c]) over the tokens of t's row, where in is
+    x + in_bias for the request's tokens and zero before its first; ``act`` "none" or "silu".  The request's last taps - 1
+    inputs are kept at state[slot, conv_offset + c * (taps - 1) + j] (oldest first; zero for a new request) and brought up to
+    date after the convolution.  x [T, C] in the activation type, out [T, C] in that type or float32 (views of wider rows
+    are fine); weight float32 [C, taps]; the biases float32 [C] or None; state float32 [slots, n]."""
+    T, C = x.shape
+    taps = weight.shape[1]
+    R = state_slots.numel()
+    if act not in ("none", "silu"):
+        raise KernelError(f"causal_conv: act {act!r} (none, silu)")
+    if x.stride(1) != 1 or out.stride(1) != 1 or out.shape != x.shape or (out.dtype != x.dtype and out.dtype != torch.float32):
+        raise KernelError("causal_conv: x and out must be [T, C] with unit inner stride, out in x's type or float32")
+    for b_ in (in_bias, out_bias):
+        if b_ is not None and (b_.dtype != torch.float32 or b_.numel() != C):
+            raise KernelError("causal_conv: biases must be float32 [C]")
+    if weight.dtype != torch.float32 or weight.shape[0] != C or not weight.is_contiguous():
+        raise KernelError("causal_conv: weight float32 [C, taps] contiguous")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < conv_offset + C * (taps - 1) or state.stride(1) != 1:
+        raise KernelError("causal_conv: state must be float32 [slots, n] with room for C * (taps - 1) numbers at conv_offset")
+    _i32(q_indptr, "q_indptr"), _i32(row_of_token, "row_of_token"), _i32(state_slots, "state_slots")
+    _check(library().arle_causal_conv(_ptr(x), _dt(x), x.stride(0), _ptr(in_bias), _ptr(weight), _ptr(out_bias), int(act == "silu"),
+                                      _ptr(state), state.stride(0), int(conv_offset), _ptr(q_indptr), _ptr(row_of_token),
+                                      _ptr(state_slots), _ptr(out), _dt(out), out.stride(0), T, R, C, taps, _stream()), "causal_conv")
+    if taps > 1:
+        add_launches(1)
+
+
+def rglru_scan(z, u, y, bias_r, bias_i, lam, y_bias, c_decay: float, state, q_indptr, state_slots, out, blocks: int,
+               max_q_len: int) -> None:
+    """The real-gated linear recurrent unit over the tokens of every row of the step, from and into state[state_slots[r]]
+    (its first ``width`` numbers): r = sigmoid(z_r + bias_r), i = sigmoid(z_i + bias_i), a = exp(-c_decay * r * softplus(lam)),
+    S_t = a S_(t-1) + sqrt(1 - a^2) * i * u_t, out_t = S_t * gelu_tanh(y_t + y_bias).  z float32 [T, 2*width] contiguous, per
+    token and block of width/blocks channels the recurrence gates' sums, then the input gates'; u float32 [T, width]
+    contiguous; y, out [T, width] in the activation type (views of wider rows are fine); the rest float32 [width]."""
+    T, width = u.shape
+    R = state_slots.numel()
+    if (z.dtype != torch.float32 or tuple(z.shape) != (T, 2 * width) or not z.is_contiguous() or u.dtype != torch.float32
+            or not u.is_contiguous() or width % blocks):
+        raise KernelError("rglru_scan: z float32 [T, 2*width] and u float32 [T, width], contiguous; width a multiple of blocks")
+    if tuple(y.shape) != (T, width) or tuple(out.shape) != (T, width) or y.stride(1) != 1 or out.stride(1) != 1 or y.dtype != out.dtype:
+        raise KernelError("rglru_scan: y and out must be [T, width] of one type with unit inner stride")
+    for t_ in (bias_r, bias_i, lam) + ((y_bias,) if y_bias is not None else ()):
+        if t_.dtype != torch.float32 or t_.numel() != width or not t_.is_contiguous():
+            raise KernelError("rglru_scan: biases and lam must be contiguous float32 [width]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < width or state.stride(1) != 1:
+        raise KernelError("rglru_scan: state must be float32 [slots, >= width]")
+    _i32(q_indptr, "q_indptr"), _i32(state_slots, "state_slots")
+    if q_indptr.numel() != R + 1:
+        raise KernelError("rglru_scan: q_indptr must have one entry more than state_slots")
+    _check(library().arle_rglru_scan(_ptr(z), _ptr(u), _ptr(y), _dt(y), y.stride(0), _ptr(bias_r), _ptr(bias_i), _ptr(lam), _ptr(y_bias),
+                                     float(c_decay), _ptr(state), state.stride(0), _ptr(q_indptr), _ptr(state_slots), _ptr(out),
+                                     out.stride(0), R, width, blocks, max(int(max_q_len), 1), _stream()), "rglru_scan")
+
+
+def delta_gates(pre, a_log, dt_bias, beta, decay) -> None:
+    """beta = sigmoid(pre[:, :H]); decay = exp(-exp(a_log) * softplus(pre[:, H:] + dt_bias)); pre float32 [T, 2H] (any row
+    stride); a_log, dt_bias float32 [H]; beta, decay float32 [T, H] contiguous."""
+    T, H = beta.shape
+    if pre.dtype != torch.float32 or pre.shape[0] != T or pre.shape[1] < 2 * H or pre.stride(1) != 1:
+        raise KernelError("delta_gates: pre must be float32 [T, >= 2H] with unit inner stride")
+    for t_ in (a_log, dt_bias):
+        if t_.dtype != torch.float32 or t_.numel() != H:
+            raise KernelError("delta_gates: a_log and dt_bias must be float32 [H]")
+    for t_ in (beta, decay):
+        if t_.dtype != torch.float32 or tuple(t_.shape) != (T, H) or not t_.is_contiguous():
+            raise KernelError("delta_gates: beta and decay must be contiguous float32 [T, H]")
+    _check(library().arle_delta_gates(_ptr(pre), pre.stride(0), _ptr(a_log), _ptr(dt_bias), _ptr(beta), _ptr(decay), T, H, _stream()),
+           "delta_gates")
+
+
+def delta_scan(q, k, v, beta, decay, state, q_indptr, state_slots, out, heads: int, kq_heads: int, dim: int, vdim: int,
+               q_scale: float, unit_eps: float) -> None:
+    """The gated delta rule over the tokens of every row of the step, from and into state[state_slots[r]]: with q and k brought
+    to unit length per head (x / sqrt(sum x^2 + unit_eps); q also times q_scale), S <- decay_t S; u = beta_t (v_t - S^T k_t);
+    S <- S + k_t u^T; o_t = S^T q_t.  q, k [T, kq_heads*dim] (head h reads head h // (heads / kq_heads)), v [T, heads*vdim], in
+    the activation type (views of wider rows are fine); beta, decay float32 [T, heads]; state float32 [slots, n] whose first
+    heads * vdim * dim numbers are the memories, a head's transposed ([heads][vdim][dim]); out float32 [T, heads, vdim]."""
+    T = v.shape[0]
+    R = state_slots.numel()
+    if (q.shape != (T, kq_heads * dim) or k.shape != q.shape or v.shape != (T, heads * vdim) or q.dtype != k.dtype
+            or q.dtype != v.dtype or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1):
+        raise KernelError("delta_scan: q, k [T, kq_heads*dim] and v [T, heads*vdim] of one type with unit inner stride")
+    for t_, n_ in ((beta, "beta"), (decay, "decay")):
+        if t_.dtype != torch.float32 or tuple(t_.shape) != (T, heads) or not t_.is_contiguous():
+            raise KernelError(f"delta_scan: {n_} must be contiguous float32 [T, heads]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < heads * vdim * dim or state.stride(1) != 1:
+        raise KernelError(f"delta_scan: state {tuple(state.shape)} must be float32 [slots, >= {heads * vdim * dim}]")
+    if out.dtype != torch.float32 or tuple(out.shape) != (T, heads, vdim) or not out.is_contiguous():
+        raise KernelError("delta_scan: out must be contiguous float32 [T, heads, vdim]")
+    _i32(q_indptr, "q_indptr"), _i32(state_slots, "state_slots")
+    if q_indptr.numel() != R + 1:
+        raise KernelError("delta_scan: q_indptr must have one entry more than state_slots")
+    _check(library().arle_delta_scan(_ptr(q), _ptr(k), _ptr(v), _dt(q), q.stride(0), k.stride(0), v.stride(0), _ptr(beta), _ptr(decay),
+                                     _ptr(state), state.stride(0), _ptr(q_indptr), _ptr(state_slots), _ptr(out), R, heads, kq_heads,
+                                     dim, vdim, float(q_scale), float(unit_eps), _stream()), "delta_scan")

@@ -15,6 +15,11 @@ is its row of W_k x before norm and rotation (kept in the cache's second stream)
 ``head_gate`` multiplies head h's output by sigmoid(W_g x)_h before the output projection
 (W_g's rows ride in the packed input projection); the position encoding's ``pairing`` chooses
 which elements turn together.  ``names`` gives the tensors' names after the prefix.
+
+``qk_norm`` "head_after_rotation" rotates first and norms after (per head; ``qk_norm_weight`` False: x / rms(x) without a
+stored weight); ``value_dim`` gives values another width than keys; ``sink`` adds a term exp(sink) without a value to the
+softmax's denominator; ``cache_window`` is what the cache keeps when other runs read this run's keys through wider windows
+than its own.
 """
 from __future__ import annotations
 
@@ -43,6 +48,11 @@ class AttentionSpec:
     values: str = "projected"       # "projected": W_v x; "keys": the keys as projected
     head_gate: bool = False         # head h's output times sigmoid(W_g x)_h
     names: Optional[Tuple[Tuple[str, str], ...]] = None    # (role, name after the prefix); see DEFAULT_NAMES
+    qk_norm_weight: bool = True     # False: the per-head norm has no stored weight
+    value_dim: Optional[int] = None  # None: head_dim
+    sink: Optional[float] = None    # score of a sink without a value in the softmax's denominator
+    cache_window: Optional[int] = None   # what the cache keeps (None: ``window``); at least ``window``
+    own_keys: bool = True           # False: no key and value projections; every run reads another run's cache
     kind: ClassVar[str] = "attention"
 
 
@@ -58,12 +68,26 @@ class Attention(Mixer):
             raise ValueError(f"head_dim {spec.head_dim} not supported (even, at most 256)")
         if spec.window is not None and spec.window <= 0:
             raise ValueError("window must be positive")
-        if spec.qk_norm not in ("head", "row") or spec.values not in ("projected", "keys"):
+        if spec.qk_norm not in ("head", "row", "head_after_rotation") or spec.values not in ("projected", "keys"):
             raise ValueError(f"attention: qk_norm {spec.qk_norm!r} / values {spec.values!r} not known")
+        self.vd = spec.head_dim if spec.value_dim is None else spec.value_dim
+        if not 0 < self.vd <= 256:
+            raise ValueError(f"attention: value_dim {self.vd} not supported (1 to 256)")
+        if spec.cache_window is not None and (spec.window is None or spec.cache_window < spec.window):
+            raise ValueError("attention: cache_window goes with a window and is at least as long")
         self.spec = spec
+        self.own_keys = spec.own_keys
+        # rotation first and norm after it, values of another width, a sink: the later form, with kernels of its own
+        self.post_form = spec.qk_norm == "head_after_rotation"
+        if self.post_form and (spec.values != "projected" or spec.head_gate):
+            raise ValueError("attention: a norm after the rotation goes with projected values and no gate")
+        if not self.post_form and (self.vd != spec.head_dim or spec.sink is not None or not spec.qk_norm_weight or not spec.own_keys):
+            raise ValueError("attention: value_dim, sink, a norm without weight and a run without keys of its own need qk_norm 'head_after_rotation'")
         self.position = build_part(spec.position) if spec.position is not None else None
         self.pairing = getattr(self.position, "pairing", "half")
         # the form the first kernels of this package were written for; everything else takes the general preparation
+        if self.post_form and self.pairing != "half":
+            raise ValueError("attention: a norm after the rotation goes with half-split rotation")
         self.plain_form = (spec.qk_norm == "head" and spec.values == "projected" and not spec.head_gate
                            and self.pairing == "half")
         if not self.plain_form and spec.qk_norm == "head" and spec.qk_norm_eps is not None:
@@ -80,6 +104,16 @@ class Attention(Mixer):
     def weight_decls(self):
         s = self.spec
         dq, dkv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        if self.post_form:
+            decls = [WeightDecl(self._name("q"), (dq, s.hidden_size))]
+            if self.own_keys:
+                decls += [WeightDecl(self._name("k"), (dkv, s.hidden_size)), WeightDecl(self._name("v"), (s.num_kv_heads * self.vd, s.hidden_size))]
+            decls.append(WeightDecl(self._name("o"), (s.hidden_size, s.num_heads * self.vd)))
+            if s.qk_norm_eps is not None and s.qk_norm_weight:
+                decls.append(WeightDecl(self._name("q_norm"), (s.head_dim,), init="gain"))
+                if self.own_keys:
+                    decls.append(WeightDecl(self._name("k_norm"), (s.head_dim,), init="gain"))
+            return tuple(decls)
         decls = [WeightDecl(self._name("q"), (dq, s.hidden_size)), WeightDecl(self._name("k"), (dkv, s.hidden_size))]
         if s.values == "projected":
             decls.append(WeightDecl(self._name("v"), (dkv, s.hidden_size)))
@@ -93,7 +127,10 @@ class Attention(Mixer):
 
     def load(self, tensors, dtype, device):
         s = self.spec
-        mats = [tensors[self._name(n)] for n in (("q", "k", "v") if s.values == "projected" else ("q", "k"))]
+        roles = ("q", "k", "v") if s.values == "projected" else ("q", "k")
+        if self.post_form and not self.own_keys:
+            roles = ("q",)
+        mats = [tensors[self._name(n)] for n in roles]
         if s.head_gate:
             self.gate_at = sum(m.shape[0] for m in mats)
             mats.append(tensors[self._name("gate")])
@@ -104,9 +141,10 @@ class Attention(Mixer):
         self.w_qkv = torch.cat([m.to(device=device, dtype=wt) for m in mats], dim=0).contiguous()
         o = tensors[self._name("o")]
         self.w_o = o.to(device=device, dtype=dtype if dtype == torch.bfloat16 else o.dtype).contiguous()
-        if s.qk_norm_eps is not None:
+        if s.qk_norm_eps is not None and s.qk_norm_weight:
             self.q_norm = tensors[self._name("q_norm")].to(device=device, dtype=torch.float32).contiguous()
-            self.k_norm = tensors[self._name("k_norm")].to(device=device, dtype=torch.float32).contiguous()
+            if self.own_keys:
+                self.k_norm = tensors[self._name("k_norm")].to(device=device, dtype=torch.float32).contiguous()
         if self.position is not None:
             self.position.load(tensors, dtype, device)
 
@@ -115,17 +153,21 @@ class Attention(Mixer):
 
     def scratch_elements_per_token(self):
         s = self.spec
-        return (3 * s.num_heads + 2 * s.num_kv_heads) * s.head_dim + s.hidden_size + 8
+        return (3 * s.num_heads + 2 * s.num_kv_heads) * max(s.head_dim, self.vd) + s.hidden_size + 8
 
     # ------------------------------------------------------------------ cache
     def cache_need(self):
-        return CacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+        s = self.spec
+        window = s.cache_window if s.cache_window is not None else s.window
+        if self.vd != s.head_dim:
+            return CacheNeed(streams=((s.num_kv_heads, s.head_dim), (s.num_kv_heads, self.vd)), window=window)
+        return CacheNeed(s.num_kv_heads, s.head_dim, window)
 
     def takes_scaled_rows(self, num_rows):
-        return ops.fused_gemm_shape_ok(num_rows, self.w_qkv)
+        return not self.post_form and ops.fused_gemm_shape_ok(num_rows, self.w_qkv)
 
     def can_sink(self, num_rows):
-        return ops.fused_gemm_shape_ok(num_rows, self.w_o)
+        return not self.post_form and ops.fused_gemm_shape_ok(num_rows, self.w_o)
 
     def _angles(self, qkv, ctx, inv_freq, rdim, general=False):
         """Cosines and sines of the step's positions, evaluated once for all layers that rotate by the same
@@ -141,9 +183,31 @@ class Attention(Mixer):
             ctx.memo[key] = angles
         return angles
 
+    # ------------------------------------------------- rotation first, norm after it
+    def _forward_post(self, x, ctx, cache):
+        s = self.spec
+        T = x.shape[0]
+        nq, nkv, hd, vd = s.num_heads, s.num_kv_heads, s.head_dim, self.vd
+        rot = self.position.rotary() if self.position is not None else None
+        inv_freq, rdim = rot if rot is not None else (None, 0)
+        if cache.writable != self.own_keys:
+            raise RuntimeError("attention: a run without key and value projections must read another run's cache, and only such a run")
+        kv = nkv if cache.writable else 0
+        proj = ctx.ws.get("qkv", (T, self.w_qkv.shape[0]), x.dtype)
+        ops.gemm(x, self.w_qkv, proj)
+        ops.attention_prep_post(proj, ctx.positions, cache.slot_mapping if kv else None, self.q_norm, self.k_norm if kv else None,
+                                s.qk_norm_eps, inv_freq, rdim, cache.k if kv else None, cache.v if kv else None, nq, kv, hd, vd,
+                                cache.page_size)
+        attn = ctx.ws.get("attn_out", (T, nq * vd), x.dtype)
+        ops.paged_attention(proj[:, : nq * hd], attn, cache.k, cache.v, ctx.positions, ctx.row_of_token, cache.block_table,
+                            nq, nkv, hd, cache.page_size, s.scale, s.window, batch=ctx, vd=vd, sink=s.sink)
+        out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)
+        ops.gemm(attn, self.w_o, out)
+        return out
+
     # ------------------------------------------------- the general form, up to the output projection
     def pre_output_width(self):
-        return self.spec.num_heads * self.spec.head_dim
+        return self.spec.num_heads * self.vd
 
     def output_weight(self):
         return self.w_o
@@ -184,6 +248,8 @@ class Attention(Mixer):
     def forward(self, x, ctx, cache, state, sink=None):
         s = self.spec
         T = x.shape[0]
+        if self.post_form:
+            return self._forward_post(x, ctx, cache)
         if not self.plain_form:
             attn, proj = self._attend(x, ctx, cache)
             if s.head_gate:

@@ -78,3 +78,56 @@ class PreNormBlock(Block):
 
 
 register_part(PreNormBlockSpec.kind, PreNormBlock)
+
+
+@dataclass(frozen=True)
+class OutputNormBlockSpec:
+    """x <- x + norm(mixer(x)); x <- x + norm(ffn(x)): the norms stand on the sublayers' outputs, the sublayers read the
+    residual as it is (the second half is absent when the spec names no feed-forward)."""
+    mixer_norm: object
+    mixer: object
+    ffn_norm: object = None
+    ffn: object = None
+    kind: ClassVar[str] = "outnorm_block"
+
+
+class OutputNormBlock(Block):
+    """The norm needs ``add_normed(resid, branch, copy)`` (``RmsNorm`` has it): the branch's norm, the sum into the 32-bit
+    residual and the rounded copy that the next sublayer reads are one kernel."""
+
+    def __init__(self, spec: OutputNormBlockSpec):
+        self.spec = spec
+        self.mixer_norm = build_part(spec.mixer_norm)
+        self.mixer = build_part(spec.mixer)
+        if (spec.ffn is None) != (spec.ffn_norm is None):
+            raise ValueError("a block has a feed-forward and its norm, or neither")
+        self.ffn_norm = build_part(spec.ffn_norm) if spec.ffn_norm is not None else None
+        self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
+        self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ValueError(f"norm {type(n).__name__} cannot stand on a branch's output (no add_normed)")
+
+    def weight_decls(self):
+        return tuple(d for p in self._parts for d in p.weight_decls())
+
+    def load(self, tensors, dtype, device):
+        for p in self._parts:
+            p.load(tensors, dtype, device)
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self._parts)
+
+    def scratch_elements_per_token(self):
+        width = self.mixer_norm.scratch_elements_per_token()
+        return 2 * width + max(self.mixer.scratch_elements_per_token(), self.ffn.scratch_elements_per_token() if self.ffn is not None else 0)
+
+    def forward(self, stream, ctx, cache, state):
+        h = stream.plain("plain_a")
+        stream.add_normed(self.mixer_norm, self.mixer.forward(h, ctx, cache, state), "plain_b")
+        if self.ffn is not None:
+            h = stream.plain("plain_b")
+            stream.add_normed(self.ffn_norm, self.ffn.forward(h, ctx), "plain_a")
+
+
+register_part(OutputNormBlockSpec.kind, OutputNormBlock)

@@ -39,6 +39,7 @@ class ResidualStream:
         self.next_entry = None
         self._sink = None
         self._sinks_made = 0
+        self._copy: Optional[torch.Tensor] = None       # the residual as it stands, in the activation type (or None)
 
     def add(self, delta: Optional[torch.Tensor]) -> None:
         """``delta`` None: the branch has already put its output into the residual (through a sink)."""
@@ -47,6 +48,31 @@ class ResidualStream:
         if self.pending is not None:
             ops.residual_add(self.resid, self.pending)
         self.pending = delta
+        self._copy = None
+
+    # Blocks whose norms stand on the branches' outputs: the sublayers read the residual as it is.
+    def plain(self, buffer_name: str) -> torch.Tensor:
+        """The residual as a sublayer's input: itself in float32, its rounding to the activation type otherwise
+        (written by the ``add_normed`` before it, or by a pass of its own at the model's first block)."""
+        if self.pending is not None:
+            ops.residual_add(self.resid, self.pending)
+            self.pending = None
+            self._copy = None
+        if self.act_dtype == torch.float32:
+            return self.resid
+        if self._copy is None:
+            self._copy = self.ws.get(buffer_name, tuple(self.resid.shape), self.act_dtype)
+            ops.branch_norm_add(self.resid, None, None, 0.0, self._copy)
+        return self._copy
+
+    def add_normed(self, norm, branch: torch.Tensor, buffer_name: str) -> None:
+        """resid += norm(branch), and the rounded residual for whoever reads it next, in one kernel."""
+        if self.pending is not None:
+            ops.residual_add(self.resid, self.pending)
+            self.pending = None
+        copy = None if self.act_dtype == torch.float32 else self.ws.get(buffer_name, tuple(self.resid.shape), self.act_dtype)
+        norm.add_normed(self.resid, branch, copy)
+        self._copy = copy
 
     def sink_for(self, norm, reader, buffer_name: str):
         """A sink for the branch that runs now, if the norm that follows it can be deferred and its
@@ -76,6 +102,8 @@ class ResidualStream:
                 return ops.ScaledRows(sink.xs, sink.ss, sink.eps)
         out = self.ws.get(buffer_name, tuple(self.resid.shape), self.act_dtype)
         norm.apply(self.resid, self.pending, None, out, write_resid=self.pending is not None)
+        if self.pending is not None:
+            self._copy = None
         self.pending = None
         return out
 

@@ -7,6 +7,10 @@ neighbours; a group's score is the sum of its two largest choice scores and only
 chosen.  An optional shared expert (a gated feed-forward of its own size) runs for every token and is added, times
 sigmoid(w_sg . x), one number per token, when it has such a gate.
 
+Variants, each a field of the spec: ``scores`` "softmax" takes the scores as a softmax over all experts; ``group_score``
+"max" scores a group by its largest choice score alone; ``activation`` "clamped_glu" makes an expert
+down(g * sigmoid(act_alpha * g) * (u + 1)) with g = min(gate x, act_limit) and u = up x clamped to +-act_limit.
+
 The step's (token, choice) pairs are sorted by expert on the device and the experts' products run as grouped tiles over
 the sorted places, so nothing depends on the host knowing how many tokens an expert got (a decode step stays capturable).
 The shared gate's row rides in the router's product.
@@ -38,6 +42,10 @@ class RoutedExpertsSpec:
     shared_gate: bool = False        # the shared expert's output times sigmoid(w . x)
     activation: str = "silu"
     names: Optional[Tuple[Tuple[str, str], ...]] = None    # (role, name after the prefix); see DEFAULT_NAMES
+    scores: str = "sigmoid"          # or "softmax" (over all experts)
+    group_score: str = "top2_sum"    # or "max"
+    act_limit: Optional[float] = None    # of the "clamped_glu" activation
+    act_alpha: float = 1.702
     kind: ClassVar[str] = "routed_experts"
 
 
@@ -52,8 +60,12 @@ class RoutedExperts(FeedForward):
             raise ValueError("routed experts: experts must split into the groups, of which at most all are kept")
         if spec.top > spec.keep * per or E > 1024:
             raise ValueError("routed experts: more experts chosen than the kept groups hold, or more than 1,024 experts")
-        if spec.activation not in ops.ACTIVATIONS:
+        if spec.activation not in ops.ACTIVATIONS and spec.activation != "clamped_glu":
             raise ValueError(f"routed experts: activation {spec.activation!r}")
+        if spec.activation == "clamped_glu" and not (spec.act_limit is not None and spec.act_limit > 0):
+            raise ValueError("routed experts: the clamped activation needs a positive act_limit")
+        if spec.scores not in ("sigmoid", "softmax") or spec.group_score not in ("top2_sum", "max"):
+            raise ValueError(f"routed experts: scores {spec.scores!r} / group_score {spec.group_score!r} not known")
         if spec.shared_gate and spec.shared is None:
             raise ValueError("routed experts: a shared gate needs a shared expert")
         self.spec = spec
@@ -121,7 +133,7 @@ class RoutedExperts(FeedForward):
         ids = ctx.ws.get("moe_ids", (T, top), torch.int32)
         weights = ctx.ws.get("moe_weights", (T, top), torch.float32)
         ops.moe_select(z, self.correction, ctx.ws.get("moe_scratch", (T, E + s.groups), torch.float32), E, top, s.groups, s.keep,
-                       s.route_scale, ids, weights)
+                       s.route_scale, ids, weights, scores=s.scores, group_score=s.group_score)
         plan = ctx.ws.get("moe_plan", (ops.moe_plan_size(E, pairs),), torch.int32)
         place_of_pair = ctx.ws.get("moe_place", (pairs,), torch.int32)
         row_of_place = ctx.ws.get("moe_row", (pairs,), torch.int32)
@@ -129,7 +141,10 @@ class RoutedExperts(FeedForward):
         gu = ctx.ws.get("moe_gate_up", (pairs, 2 * ff), x.dtype)
         ops.moe_gemm(x, row_of_place, self.w_gate_up, gu, plan, E)
         act = ctx.ws.get("moe_act", (pairs, ff), x.dtype)
-        ops.act_mul(gu, act, s.activation)
+        if s.activation == "clamped_glu":
+            ops.clamped_glu(gu, act, s.act_limit, s.act_alpha)
+        else:
+            ops.act_mul(gu, act, s.activation)
         y = ctx.ws.get("moe_y", (pairs, s.hidden_size), x.dtype)
         ops.moe_gemm(act, None, self.w_down, y, plan, E)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None

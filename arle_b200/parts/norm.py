@@ -54,6 +54,11 @@ class RmsNorm(Norm):
         ops.rmsnorm(resid, delta, rows, self.weight, self.eps, out, write_resid)
         return out
 
+    def add_normed(self, resid, branch, copy):
+        """resid += norm(branch) (the norm on a branch's output); ``copy`` gets the new residual in its own type;
+        see ops.branch_norm_add."""
+        ops.branch_norm_add(resid, branch, self.weight, self.eps, copy)
+
 
 register_part(RmsNormSpec.kind, RmsNorm)
 

@@ -87,9 +87,10 @@ def attention_prep(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_fr
 
 
 def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_table, nq, nkv, hd, page_size, scale,
-                    window, batch=None):
+                    window, batch=None, vd=None, sink=None):
     T = q.shape[0]
     g = nq // nkv
+    vd = hd if vd is None else vd
     for t in range(T):
         p = int(positions[t])
         lo = max(0, p - window + 1) if window else 0
@@ -101,8 +102,11 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
         qt = q[t].view(nq, hd).to(F32)
         for h in range(nq):
             s = (k[:, h // g] @ qt[h]) * scale
-            pr = torch.softmax(s, dim=0)
-            out[t, h * hd:(h + 1) * hd] = (pr @ v[:, h // g]).to(out.dtype)
+            if sink is None:
+                pr = torch.softmax(s, dim=0)
+            else:                                            # one more term in the denominator, without a value
+                pr = torch.softmax(torch.cat([s, torch.tensor([float(sink)])]), dim=0)[:-1]
+            out[t, h * vd:(h + 1) * vd] = (pr @ v[:, h // g]).to(out.dtype)
 
 
 def silu_mul(gate_up, out):
@@ -380,12 +384,12 @@ def gated_group_norm(y, x, skip, vdim, z, weight, eps, out, parts):
 
 
 # ---------------------------------------------------------------- routed experts
-def moe_select(z, correction, scratch, experts, top, groups, keep, scale, ids, weights):
-    s_ = torch.sigmoid(z[:, :experts])
+def moe_select(z, correction, scratch, experts, top, groups, keep, scale, ids, weights, scores="sigmoid", group_score="top2_sum"):
+    s_ = torch.sigmoid(z[:, :experts]) if scores == "sigmoid" else torch.softmax(z[:, :experts], dim=-1)
     ch = s_ + correction if correction is not None else s_.clone()
     per = experts // groups
     g = ch.view(-1, groups, per)
-    gs = g.topk(min(2, per), dim=-1).values.sum(-1)
+    gs = g.topk(min(2, per) if group_score == "top2_sum" else 1, dim=-1).values.sum(-1)
     kept = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, gs.topk(keep, dim=-1).indices, True)
     ch = torch.where(kept[:, :, None].expand(-1, -1, per).reshape(-1, experts), ch, torch.full_like(ch, -math.inf))
     pick = ch.topk(top, dim=-1).indices
@@ -427,7 +431,107 @@ def moe_combine(y, place_of_pair, weights, shared, gate, out):
     out.copy_(acc.to(out.dtype))
 
 
+# ---------------------------------------------------------------- parts of further designs
+def clamped_glu(gate_up, out, limit, alpha):
+    g = gate_up[:, 0::2].to(F32).clamp(max=limit)
+    u = gate_up[:, 1::2].to(F32).clamp(min=-limit, max=limit)
+    out.copy_((g * torch.sigmoid(alpha * g) * (u + 1.0)).to(out.dtype))
+
+
+def branch_norm_add(resid, branch, weight, eps, copy):
+    if branch is not None:
+        b = branch.to(F32)
+        resid += b / torch.sqrt((b * b).mean(-1, keepdim=True) + eps) * weight
+    if copy is not None:
+        copy.copy_(resid.to(copy.dtype))
+
+
+def attention_prep_post(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, k_cache, v_cache,
+                        nq, nkv, hd, vd, page_size):
+    T = qkv.shape[0]
+    pos = positions.to(F32)
+
+    def prepared(x, weight):                         # x [T, heads, hd]
+        x = x.to(F32)
+        if rotary_dim:
+            x = _turn_half(x, pos, inv_freq, rotary_dim)
+        if eps is not None:
+            x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+        return x * weight if weight is not None else x
+
+    q = prepared(qkv[:, : nq * hd].view(T, nq, hd), q_weight)
+    qkv[:, : nq * hd] = q.reshape(T, nq * hd).to(qkv.dtype)
+    if nkv:
+        k = prepared(qkv[:, nq * hd: (nq + nkv) * hd].view(T, nkv, hd), k_weight).to(qkv.dtype)
+        v = qkv[:, (nq + nkv) * hd: (nq + nkv) * hd + nkv * vd].view(T, nkv, vd)
+        keep = slot_mapping >= 0
+        page, off = (slot_mapping[keep] // page_size).long(), (slot_mapping[keep] % page_size).long()
+        k_cache[page, :, off] = k[keep]
+        v_cache[page, :, off] = v[keep]
+
+
+def causal_conv(x, in_bias, weight, out_bias, act, state, conv_offset, q_indptr, row_of_token, state_slots, out):
+    C, taps = weight.shape
+    for r in range(state_slots.numel()):
+        beg, end = int(q_indptr[r]), int(q_indptr[r + 1])
+        if end == beg:
+            continue
+        hist = state[int(state_slots[r]), conv_offset: conv_offset + C * (taps - 1)].view(C, taps - 1)
+        xin = x[beg:end].to(F32) + (in_bias[None, :] if in_bias is not None else 0.0)
+        seq = torch.cat([hist.t(), xin], dim=0)                               # [taps - 1 + n, C]
+        acc = out_bias[None, :].repeat(end - beg, 1) if out_bias is not None else torch.zeros(end - beg, C)
+        for j in range(taps):
+            acc = acc + seq[j: j + end - beg] * weight[:, j][None, :]
+        out[beg:end] = (acc / (1.0 + torch.exp(-acc)) if act == "silu" else acc).to(out.dtype)
+        if taps > 1:
+            hist.copy_(seq[seq.shape[0] - (taps - 1):].t())
+
+
+def rglru_scan(z, u, y, bias_r, bias_i, lam, y_bias, c_decay, state, q_indptr, state_slots, out, blocks, max_q_len):
+    T, width = u.shape
+    bs = width // blocks
+    zz = z.view(T, blocks, 2, bs)
+    rg = torch.sigmoid(zz[:, :, 0].reshape(T, width) + bias_r)
+    ig = torch.sigmoid(zz[:, :, 1].reshape(T, width) + bias_i)
+    log_a = -c_decay * rg * torch.nn.functional.softplus(lam)
+    a = torch.exp(log_a)
+    b = torch.sqrt(-torch.expm1(2.0 * log_a)) * ig * u
+    yy = y.to(F32) + (y_bias if y_bias is not None else 0.0)
+    yy = 0.5 * yy * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (yy + 0.044715 * yy ** 3)))
+    for r in range(state_slots.numel()):
+        S = state[int(state_slots[r]), :width]
+        for t in range(int(q_indptr[r]), int(q_indptr[r + 1])):
+            S.copy_(a[t] * S + b[t])
+            out[t] = (S * yy[t]).to(out.dtype)
+
+
+def delta_gates(pre, a_log, dt_bias, beta, decay):
+    H = beta.shape[1]
+    beta.copy_(torch.sigmoid(pre[:, :H]))
+    decay.copy_(torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(pre[:, H: 2 * H] + dt_bias)))
+
+
+def delta_scan(q, k, v, beta, decay, state, q_indptr, state_slots, out, heads, kq_heads, dim, vdim, q_scale, unit_eps):
+    T = v.shape[0]
+    qq, kk = q.to(F32).view(T, kq_heads, dim), k.to(F32).view(T, kq_heads, dim)
+    qq = qq / torch.sqrt((qq * qq).sum(-1, keepdim=True) + unit_eps) * q_scale
+    kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + unit_eps)
+    vv = v.to(F32).view(T, heads, vdim)
+    rep = heads // kq_heads
+    for r in range(state_slots.numel()):
+        S = state[int(state_slots[r]), : heads * vdim * dim].view(heads, vdim, dim)         # a head's memory transposed
+        for t in range(int(q_indptr[r]), int(q_indptr[r + 1])):
+            for h in range(heads):
+                g = h // rep
+                Sh = S[h] * decay[t, h]
+                u = beta[t, h] * (vv[t, h] - Sh @ kk[t, g])
+                Sh = Sh + torch.outer(u, kk[t, g])
+                S[h] = Sh
+                out[t, h] = Sh @ qq[t, g]
+
+
 ALL = ("rotary_angles", "embedding", "rmsnorm", "residual_add", "gemm", "fused_gemm_shape_ok", "fused_decode_supported", "attention_prep_takes_angles", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample",
        "act_mul", "gemm_act_mul", "attention_prep_row", "head_gate", "weighted_sum", "logit_cap", "gla_decay", "gla_scan", "gla_out",
        "dyt_norm", "gemm_heads", "latent_prep", "latent_attention", "decay_scan", "mlstm_gates", "mlstm_out", "ssm_gates", "conv_silu",
-       "gated_group_norm", "moe_select", "moe_plan_size", "moe_plan", "moe_gemm", "moe_combine")
+       "gated_group_norm", "moe_select", "moe_plan_size", "moe_plan", "moe_gemm", "moe_combine", "clamped_glu", "branch_norm_add",
+       "attention_prep_post", "causal_conv", "rglru_scan", "delta_gates", "delta_scan")
