@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
     int bt_stride, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nq, int nkv,
-    int page_size, int ps_shift, float scale_log2, int window, int splits) {
+    int page_size, int ps_shift, float scale_log2, float sink_log2, int window, int splits) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int ROW = HD + 8;                 // padded row, in elements: 16 B more keeps ldmatrix conflict-free
@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
     }
     const int head = kvh * G + row;
     if (splits == 1) {
-      out[((size_t)t * nq + head) * HD + d] = __float2bfloat16_rn(O / L);
+      out[((size_t)t * nq + head) * HD + d] = __float2bfloat16_rn(O / (L + exp2f(sink_log2 - M)));      // sink_log2 -inf: no sink
     } else {
       const size_t pidx = ((size_t)r * nq + head) * splits + split;
       part_o[pidx * HD + d] = O;
@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
       fac[tid * 64 + sp] = f;
       L += l * f;
     }
-    invl[tid] = 1.0f / L;
+    invl[tid] = 1.0f / (L + exp2f(sink_log2 - M));
   }
   __syncthreads();
   for (int i = tid; i < G * HD; i += kThreads) {
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
 template <int HD>
 int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cache, const void* v_cache,
                   const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, float* part_o,
-                  float* part_ml, int* counters, int nq, int nkv, int page_size, float scale, int window, int rows,
+                  float* part_ml, int* counters, int nq, int nkv, int page_size, float scale, float sink, int window, int rows,
                   int splits, cudaStream_t s) {
   constexpr int ROW = HD + 8;
   int ps_shift = -1;
@@ -321,7 +321,7 @@ int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cach
   launch_kernel(paged_decode_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 1, 
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters, nq, nkv,
-      page_size, ps_shift, scale * 1.4426950408889634f, window, splits);
+      page_size, ps_shift, scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, splits);
   return launch_status();
 }
 
@@ -332,7 +332,7 @@ int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cach
 ARLE_API int arle_paged_attention_decode(const void* q, int q_row_stride, void* out, const void* k_cache,
                                          const void* v_cache, const int* q_indptr, const int* kv_lens,
                                          const int* block_table, int bt_stride, float* part_o, float* part_ml,
-                                         int* counters, int nq, int nkv, int hd, int page_size, float scale, int window,
+                                         int* counters, int nq, int nkv, int hd, int page_size, float scale, float sink, int window,
                                          int rows, int splits, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || page_size <= 0) return ARLE_E_UNSUPPORTED;
@@ -341,9 +341,9 @@ ARLE_API int arle_paged_attention_decode(const void* q, int q_row_stride, void* 
   if ((q_row_stride % 8) != 0) return ARLE_E_UNSUPPORTED;     // 16-byte loads of q rows
   if (hd == 128)
     return launch_decode<128>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o,
-                              part_ml, counters, nq, nkv, page_size, scale, window, rows, splits, s);
+                              part_ml, counters, nq, nkv, page_size, scale, sink, window, rows, splits, s);
   if (hd == 64)
     return launch_decode<64>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o,
-                             part_ml, counters, nq, nkv, page_size, scale, window, rows, splits, s);
+                             part_ml, counters, nq, nkv, page_size, scale, sink, window, rows, splits, s);
   return ARLE_E_UNSUPPORTED;
 }

@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
     const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table, int bt_stride,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int R, int nq, int nkv,
-    int bt_width, int page_size, int ps_shift, float scale_log2, int window, int stages, Prep prep, const int* __restrict__ plan,
+    int bt_width, int page_size, int ps_shift, float scale_log2, float sink_log2, int window, int stages, Prep prep, const int* __restrict__ plan,
     int* __restrict__ err) {
   pdl_launch_dependents();
   pdl_wait();
@@ -611,7 +611,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
           O += mo[(w * G + row) * HD + d] * f;
         }
         if (pieces == 1) {
-          out[((size_t)t * nq + kvh * G + row) * HD + d] = __float2bfloat16_rn(O / L);
+          out[((size_t)t * nq + kvh * G + row) * HD + d] = __float2bfloat16_rn(O / (L + exp2f(sink_log2 - M)));   // sink_log2 -inf: no sink
         } else {
           part_o[((size_t)slot * G + row) * HD + d] = O;
           if (d == 0) {
@@ -660,7 +660,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
                 }
               }
             }
-            const float inv = 1.0f / L;
+            const float inv = 1.0f / (L + exp2f(sink_log2 - M));
             *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)t * nq + kvh * G + row) * HD + d) = __floats2bfloat162_rn(O0 * inv, O1 * inv);
           }
         }
@@ -682,7 +682,7 @@ size_t fixed_smem(int G, int hd, int ctas, int R) {
 template <int HD>
 int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_row_stride, void* out,
                   const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, float* part_o,
-                  float* part_ml, int* counters, int rows, int nq, int nkv, int bt_width, int page_size, float scale, int window,
+                  float* part_ml, int* counters, int rows, int nq, int nkv, int bt_width, int page_size, float scale, float sink, int window,
                   int ctas, const Prep& prep, const int* plan, int* err, cudaStream_t s) {
   int ps_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
@@ -709,7 +709,7 @@ int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, i
   if (e != cudaSuccess) return (int)e;
   e = launch_kernel(decode_stream_kernel<HD>, dim3(ctas), dim3(kThreads), smem, s, 1, mk, mv, (const __nv_bfloat16*)q,
                     q_row_stride, (__nv_bfloat16*)out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
-                    rows, nq, nkv, bt_width, page_size, ps_shift, scale * 1.4426950408889634f, window, stages, prep, plan, err);
+                    rows, nq, nkv, bt_width, page_size, ps_shift, scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, stages, prep, plan, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }
@@ -720,7 +720,7 @@ ARLE_API int arle_paged_attention_decode_stream_prep(const void* q, int q_row_st
                                                      const void* v_cache, long long cache_pages, const int* q_indptr,
                                                      const int* kv_lens, const int* block_table, int bt_stride, int bt_width,
                                                      float* part_o, float* part_ml, int* counters, int nq, int nkv, int hd,
-                                                     int page_size, float scale, int window, int rows, int ctas, int fused,
+                                                     int page_size, float scale, float sink, int window, int rows, int ctas, int fused,
                                                      const int* slot_mapping, const float* q_weight, const float* k_weight,
                                                      float eps, const float* inv_freq, const int* plan, int* err, cudaStream_t s);
 
@@ -733,11 +733,11 @@ ARLE_API int arle_paged_attention_decode_stream(const void* q, int q_row_stride,
                                                 const void* v_cache, long long cache_pages, const int* q_indptr,
                                                 const int* kv_lens, const int* block_table, int bt_stride, int bt_width,
                                                 float* part_o, float* part_ml, int* counters, int nq, int nkv, int hd,
-                                                int page_size, float scale, int window, int rows, int ctas, int* err,
+                                                int page_size, float scale, float sink, int window, int rows, int ctas, int* err,
                                                 cudaStream_t s) {
   return arle_paged_attention_decode_stream_prep(q, q_row_stride, out, k_cache, v_cache, cache_pages, q_indptr, kv_lens,
                                                  block_table, bt_stride, bt_width, part_o, part_ml, counters, nq, nkv, hd,
-                                                 page_size, scale, window, rows, ctas, 0, nullptr, nullptr, nullptr, 0.f, nullptr,
+                                                 page_size, scale, sink, window, rows, ctas, 0, nullptr, nullptr, nullptr, 0.f, nullptr,
                                                  nullptr, err, s);
 }
 
@@ -765,7 +765,7 @@ ARLE_API int arle_paged_attention_decode_stream_prep(const void* q, int q_row_st
                                                      const void* v_cache, long long cache_pages, const int* q_indptr,
                                                      const int* kv_lens, const int* block_table, int bt_stride, int bt_width,
                                                      float* part_o, float* part_ml, int* counters, int nq, int nkv, int hd,
-                                                     int page_size, float scale, int window, int rows, int ctas, int fused,
+                                                     int page_size, float scale, float sink, int window, int rows, int ctas, int fused,
                                                      const int* slot_mapping, const float* q_weight, const float* k_weight,
                                                      float eps, const float* inv_freq, const int* plan, int* err, cudaStream_t s) {
   if (rows <= 0) return 0;
@@ -786,7 +786,7 @@ ARLE_API int arle_paged_attention_decode_stream_prep(const void* q, int q_row_st
   if (rc) return rc;
   if (hd == 128)
     return launch_stream<128>(mk, mv, q, q_row_stride, out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
-                              rows, nq, nkv, bt_width, page_size, scale, window, ctas, prep, plan, err, s);
+                              rows, nq, nkv, bt_width, page_size, scale, sink, window, ctas, prep, plan, err, s);
   return launch_stream<64>(mk, mv, q, q_row_stride, out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
-                           rows, nq, nkv, bt_width, page_size, scale, window, ctas, prep, plan, err, s);
+                           rows, nq, nkv, bt_width, page_size, scale, sink, window, ctas, prep, plan, err, s);
 }

@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
-    int bt_stride, int nq, int nkv, int page_size, int ps_shift, float scale_log2, int window, int skip_single) {
+    int bt_stride, int nq, int nkv, int page_size, int ps_shift, float scale_log2, float sink_log2, int window, int skip_single) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int ROW = HD + 8;
@@ -220,7 +220,8 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
+  // a sink's term in the denominator (its score in log2 units; -inf: none, and the sums stay as they are)
+  const float inv0 = 1.0f / (l0 + exp2f(sink_log2 - m0)), inv1 = 1.0f / (l1 + exp2f(sink_log2 - m1));
   const int row0 = mbeg + warp * 16 + g, row1 = row0 + 8;
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) {
@@ -238,7 +239,7 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
 template <int HD>
 int launch_prefill(const void* q, int q_row_stride, void* out, const void* k_cache, const void* v_cache,
                    const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, int nq, int nkv,
-                   int page_size, float scale, int window, int rows, int max_q_len, int skip_single, cudaStream_t s) {
+                   int page_size, float scale, float sink, int window, int rows, int max_q_len, int skip_single, cudaStream_t s) {
   constexpr int ROW = HD + 8;
   int ps_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
@@ -254,7 +255,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, const void* k_cac
   launch_kernel(paged_prefill_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 1, 
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, nq, nkv, page_size, ps_shift,
-      scale * 1.4426950408889634f, window, skip_single);
+      scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, skip_single);
   return launch_status();
 }
 
@@ -263,16 +264,16 @@ int launch_prefill(const void* q, int q_row_stride, void* out, const void* k_cac
 ARLE_API int arle_paged_attention_prefill(const void* q, int q_row_stride, void* out, const void* k_cache,
                                           const void* v_cache, const int* q_indptr, const int* kv_lens,
                                           const int* block_table, int bt_stride, int nq, int nkv, int hd, int page_size,
-                                          float scale, int window, int rows, int max_q_len, int skip_single,
+                                          float scale, float sink, int window, int rows, int max_q_len, int skip_single,
                                           cudaStream_t s) {
   if (rows <= 0 || max_q_len <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || nq > 65535 || rows > 65535) return ARLE_E_UNSUPPORTED;
   if ((q_row_stride % 8) != 0) return ARLE_E_UNSUPPORTED;
   if (hd == 128)
     return launch_prefill<128>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, nq,
-                               nkv, page_size, scale, window, rows, max_q_len, skip_single, s);
+                               nkv, page_size, scale, sink, window, rows, max_q_len, skip_single, s);
   if (hd == 64)
     return launch_prefill<64>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, nq,
-                              nkv, page_size, scale, window, rows, max_q_len, skip_single, s);
+                              nkv, page_size, scale, sink, window, rows, max_q_len, skip_single, s);
   return ARLE_E_UNSUPPORTED;
 }

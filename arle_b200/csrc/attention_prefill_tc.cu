@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, const int* __restrict__ q_indptr,
     const int* __restrict__ kv_lens, const int* __restrict__ block_table, int bt_stride, int bt_width, int nq, int nkv,
-    int page_size, float scale_log2, int window, int skip_single, int nyb, int nblocks, int ticket_slot, int* __restrict__ err) {
+    int page_size, float scale_log2, float sink_log2, int window, int skip_single, int nyb, int nblocks, int ticket_slot, int* __restrict__ err) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ unsigned char smem_dyn[];
@@ -550,7 +550,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       if (ok && n > 0) {
         ++o_all;
         tc_fence_after();
-        const float inv = 1.0f / l;
+        // a sink's term in the denominator (its score in log2 units; -inf: none, and the sum stays as it is)
+        const float inv = 1.0f / (l + exp2f(sink_log2 - (m_used == -INFINITY ? 0.f : m_used)));
         __nv_bfloat16* orow = out + ((size_t)(blk.t0 + blk.mbeg + x * BQ + row) * nq + blk.h) * HD;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -596,7 +597,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
 ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, int num_tokens, void* out, const void* k_cache,
                                              const void* v_cache, long long cache_pages, const int* q_indptr,
                                              const int* kv_lens, const int* block_table, int bt_stride, int bt_width, int nq, int nkv,
-                                             int hd, int page_size, float scale, int window, int rows, int max_q_len,
+                                             int hd, int page_size, float scale, float sink, int window, int rows, int max_q_len,
                                              int skip_single, int* err, cudaStream_t s) {
   if (rows <= 0 || max_q_len <= 0) return 0;
   if (bt_width < 1) return ARLE_E_BADARG;
@@ -631,7 +632,7 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
   const int ticket_slot = (int)(launches++ % kTicketSlots);
   cudaError_t e = launch_kernel(paged_prefill_tc_kernel, dim3(ctas), dim3(kThreads), smem, s, 1, mq, mk, mv, (__nv_bfloat16*)out,
                                 q_indptr, kv_lens, block_table, bt_stride, bt_width, nq, nkv, page_size,
-                                scale * 1.4426950408889634f, window, skip_single, nyb, (int)nblocks, ticket_slot, err);
+                                scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, skip_single, nyb, (int)nblocks, ticket_slot, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }

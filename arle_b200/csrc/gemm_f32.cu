@@ -153,19 +153,23 @@ __global__ void __launch_bounds__(256) gemm_heads_kernel(const TA* __restrict__ 
   }
 }
 
-// dtype: 0 float32 A and C (W float32 or bfloat16 by w_dtype), 1 bfloat16 A, W and C.
-ARLE_API int arle_gemm_heads(const void* A, const void* W, void* C, int dtype, int w_dtype, int M, int N, int K, int heads,
+// dtype: 0 float32 A and C (W float32 or bfloat16 by w_dtype), 1 bfloat16 A and W, C bfloat16 or (c_dtype 0) float32.
+ARLE_API int arle_gemm_heads(const void* A, const void* W, void* C, int dtype, int w_dtype, int c_dtype, int M, int N, int K, int heads,
                              int lda, int ldw, int ldc, int a_head, long w_head, int c_head, cudaStream_t s) {
   if (M <= 0 || N <= 0 || heads <= 0) return 0;
   if (K <= 0) return ARLE_E_BADARG;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, heads);
   if (grid.y > 65535 || heads > 65535) return ARLE_E_UNSUPPORTED;
+  if (dtype == 0 && c_dtype != 0) return ARLE_E_BADARG;
   if (dtype == 0 && w_dtype == 0)
     launch_kernel(gemm_heads_kernel<float, float, float>, dim3(grid), dim3(256), 0, s, 1, (const float*)A, (const float*)W,
                   (float*)C, M, N, K, lda, ldw, ldc, a_head, w_head, c_head);
   else if (dtype == 0 && w_dtype == 1)
     launch_kernel(gemm_heads_kernel<float, __nv_bfloat16, float>, dim3(grid), dim3(256), 0, s, 1, (const float*)A,
                   (const __nv_bfloat16*)W, (float*)C, M, N, K, lda, ldw, ldc, a_head, w_head, c_head);
+  else if (dtype == 1 && w_dtype == 1 && c_dtype == 0)
+    launch_kernel(gemm_heads_kernel<__nv_bfloat16, __nv_bfloat16, float>, dim3(grid), dim3(256), 0, s, 1,
+                  (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (float*)C, M, N, K, lda, ldw, ldc, a_head, w_head, c_head);
   else if (dtype == 1 && w_dtype == 1)
     launch_kernel(gemm_heads_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, s, 1,
                   (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc, a_head, w_head, c_head);

@@ -214,8 +214,9 @@ constexpr int TM = 64, TN = 128, TK = 32, TPITCH = 40, kStages = 3;
 
 // A tile of 64 rows x 128 columns of C = A . W^T on the tensor cores: row r of the tile is row arow[r] of A (-1: none) and
 // row crow0 + r of C; M rows are live.  Three stages of cp.async, one barrier a stage, eight warps of 32 x 32, mma.sync with float32 sums.
+template <typename TC>
 __device__ __forceinline__ void mma_tile_64x128(const __nv_bfloat16* __restrict__ A, int lda, const int* arow, const __nv_bfloat16* __restrict__ W,
-                                                int ldw, __nv_bfloat16* __restrict__ C, int ldc, size_t crow0, int M, int n0, int N, int K,
+                                                int ldw, TC* __restrict__ C, int ldc, size_t crow0, int M, int n0, int N, int K,
                                                 __nv_bfloat16 (*As)[TM * TPITCH], __nv_bfloat16 (*Ws)[TN * TPITCH]) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp & 1, wn = warp >> 1;
@@ -281,9 +282,9 @@ __device__ __forceinline__ void mma_tile_64x128(const __nv_bfloat16* __restrict_
         const int m = wm * 32 + mt * 16 + g + half * 8;
         const int col = n0 + wn * 32 + nt * 8 + 2 * t4;
         if (m >= M) continue;
-        __nv_bfloat16* cp = C + (crow0 + m) * ldc + col;
-        if (col < N) cp[0] = __float2bfloat16_rn(acc[mt][nt][2 * half]);
-        if (col + 1 < N) cp[1] = __float2bfloat16_rn(acc[mt][nt][2 * half + 1]);
+        TC* cp = C + (crow0 + m) * ldc + col;
+        if (col < N) cp[0] = from_f32<TC>(acc[mt][nt][2 * half]);
+        if (col + 1 < N) cp[1] = from_f32<TC>(acc[mt][nt][2 * half + 1]);
       }
 }
 
@@ -307,9 +308,10 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* 
 
 // The same tile for one matrix per head, heads side by side in the rows of A and C (see arle_gemm_heads): grid (column
 // tiles, row tiles, heads).
+template <typename TC>
 __global__ void __launch_bounds__(256) gemm_heads_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int a_head,
                                                              const __nv_bfloat16* __restrict__ W, int ldw, long w_head,
-                                                             __nv_bfloat16* __restrict__ C, int ldc, int c_head, int M, int N, int K) {
+                                                             TC* __restrict__ C, int ldc, int c_head, int M, int N, int K) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ __align__(16) __nv_bfloat16 As[kStages][TM * TPITCH];
@@ -322,16 +324,20 @@ __global__ void __launch_bounds__(256) gemm_heads_mma_kernel(const __nv_bfloat16
                   min(TM, M - m0), blockIdx.x * TN, N, K, As, Ws);
 }
 
-// bfloat16, K and every stride a multiple of 8 elements, bases on 16-byte boundaries.
-ARLE_API int arle_gemm_heads_mma(const void* A, const void* W, void* C, int M, int N, int K, int heads, int lda, int ldw, int ldc,
+// bfloat16 A and W, K and every stride a multiple of 8 elements, bases on 16-byte boundaries; C bfloat16 or (c_dtype 0) float32.
+ARLE_API int arle_gemm_heads_mma(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int heads, int lda, int ldw, int ldc,
                                  int a_head, long w_head, int c_head, cudaStream_t s) {
   if (M <= 0 || N <= 0 || heads <= 0) return 0;
   if (K <= 0) return ARLE_E_BADARG;
   if (K % 8 || lda % 8 || ldw % 8 || a_head % 8 || w_head % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return ARLE_E_UNSUPPORTED;
   dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, heads);
   if (grid.y > 65535 || heads > 65535) return ARLE_E_UNSUPPORTED;
-  launch_kernel(gemm_heads_mma_kernel, dim3(grid), dim3(256), 0, s, 1, (const __nv_bfloat16*)A, lda, a_head, (const __nv_bfloat16*)W,
-                ldw, w_head, (__nv_bfloat16*)C, ldc, c_head, M, N, K);
+  if (c_dtype == 0)
+    launch_kernel(gemm_heads_mma_kernel<float>, dim3(grid), dim3(256), 0, s, 1, (const __nv_bfloat16*)A, lda, a_head, (const __nv_bfloat16*)W,
+                  ldw, w_head, (float*)C, ldc, c_head, M, N, K);
+  else
+    launch_kernel(gemm_heads_mma_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, 1, (const __nv_bfloat16*)A, lda, a_head,
+                  (const __nv_bfloat16*)W, ldw, w_head, (__nv_bfloat16*)C, ldc, c_head, M, N, K);
   return launch_status();
 }
 

@@ -101,7 +101,7 @@ constexpr int kLruChannels = 32;          // and up to 32 segments: 1,024 thread
 constexpr int kLruMaxSeg = 8;          // tokens a thread holds at a time
 
 template <typename T>
-__global__ void __launch_bounds__(kLruChannels * 32) rglru_scan_kernel(const float* __restrict__ z, const float* __restrict__ u, const T* __restrict__ y, int y_stride,
+__global__ void __launch_bounds__(kLruChannels * 32) rglru_scan_kernel(const float* __restrict__ z, const T* __restrict__ u, const T* __restrict__ y, int y_stride,
                                   const float* __restrict__ bias_r, const float* __restrict__ bias_i, const float* __restrict__ lam,
                                   const float* __restrict__ y_bias, float c_decay, float* __restrict__ state, long slot_stride,
                                   const int* __restrict__ q_indptr, const int* __restrict__ state_slots, T* __restrict__ out,
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(kLruChannels * 32) rglru_scan_kernel(const flo
         const float log_a = -c_decay * rg * sp_lam;
         const float at = expf(log_a);
         a[j] = at;
-        b[j] = sqrtf(-expm1f(2.0f * log_a)) * ig * u[(size_t)t * width + c];      // sqrt(1 - a^2), exact near a = 1
+        b[j] = sqrtf(-expm1f(2.0f * log_a)) * ig * to_f32(u[(size_t)t * width + c]);      // sqrt(1 - a^2), exact near a = 1
       }
       A *= a[j];
       B = fmaf(a[j], B, b[j]);
@@ -177,10 +177,10 @@ __global__ void __launch_bounds__(kLruChannels * 32) rglru_scan_kernel(const flo
   if (live && seg == 0 && end > beg) *sp = S;
 }
 
-// z float32 [T, 2 * width] contiguous ([blocks][recurrence gates bs | input gates bs] per token); u float32 [T, width] contiguous;
+// z float32 [T, 2 * width] contiguous ([blocks][recurrence gates bs | input gates bs] per token); u [T, width] contiguous and
 // y, out [T, width] in the activation type (row strides given); biases, lam float32 [width]; state: float32, a slot every
 // slot_stride numbers, the channels' states at its start.  max_q_len: the most tokens any row of the step has.
-ARLE_API int arle_rglru_scan(const float* z, const float* u, const void* y, int dtype, int y_stride, const float* bias_r,
+ARLE_API int arle_rglru_scan(const float* z, const void* u, const void* y, int dtype, int y_stride, const float* bias_r,
                              const float* bias_i, const float* lam, const float* y_bias, float c_decay, float* state, long slot_stride,
                              const int* q_indptr, const int* state_slots, void* out, int out_stride, int R, int width, int blocks,
                              int max_q_len, cudaStream_t s) {
@@ -190,10 +190,10 @@ ARLE_API int arle_rglru_scan(const float* z, const float* u, const void* y, int 
   while (nseg < 32 && nseg * kLruMaxSeg < max_q_len) nseg <<= 1;
   dim3 grid((width + kLruChannels - 1) / kLruChannels, R), block(kLruChannels, nseg);
   if (dtype == 0)
-    launch_kernel(rglru_scan_kernel<float>, dim3(grid), dim3(block), 0, s, 1, z, u, (const float*)y, y_stride, bias_r, bias_i, lam, y_bias,
+    launch_kernel(rglru_scan_kernel<float>, dim3(grid), dim3(block), 0, s, 1, z, (const float*)u, (const float*)y, y_stride, bias_r, bias_i, lam, y_bias,
                   c_decay, state, slot_stride, q_indptr, state_slots, (float*)out, out_stride, width, width / blocks);
   else if (dtype == 1)
-    launch_kernel(rglru_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(block), 0, s, 1, z, u, (const __nv_bfloat16*)y, y_stride, bias_r, bias_i,
+    launch_kernel(rglru_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(block), 0, s, 1, z, (const __nv_bfloat16*)u, (const __nv_bfloat16*)y, y_stride, bias_r, bias_i,
                   lam, y_bias, c_decay, state, slot_stride, q_indptr, state_slots, (__nv_bfloat16*)out, out_stride, width, width / blocks);
   else
     return ARLE_E_BADARG;

@@ -61,15 +61,15 @@ _SIGNATURES = {
     "arle_delta_gates": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
     "arle_delta_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
     "arle_clamped_glu": [_P, _P, _I, _I, _I, _I, _F, _F, _P],
-    "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
     "arle_paged_attention_decode_stream": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
-                                           _F, _I, _I, _I, _P, _P],
+                                           _F, _F, _I, _I, _I, _P, _P],
     "arle_paged_attention_decode_stream_prep": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
-                                                _F, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P],
+                                                _F, _F, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P],
     "arle_decode_stream_plan_ints": [_I, _I],
     "arle_decode_stream_plan": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
-    "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I,
+    "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _P],
+    "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I,
                                         _I, _I, _I, _P, _P],
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "arle_gemm_plain_bf16": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -82,8 +82,8 @@ _SIGNATURES = {
     "arle_scatter_tokens": [_P, _P, _P, _I, _P],
     "arle_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "arle_dyt_norm": [_P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _P],
-    "arle_gemm_heads_mma": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_long, _I, _P],
-    "arle_gemm_heads": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_long, _I, _P],
+    "arle_gemm_heads_mma": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_long, _I, _P],
+    "arle_gemm_heads": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_long, _I, _P],
     "arle_latent_prep": [_P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_latent_attention": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
@@ -526,7 +526,8 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
 
     ``vd``: the values' width when it differs from the keys' (the value cache is then [pages, nkv, page_size, vd] and
     out [T, nq*vd]).  ``sink``: the score of a sink without a value that the softmax's denominator counts besides the
-    keys, p_j = exp(s_j) / (exp(sink) + sum exp(s_j)); None for the usual softmax.  Both run on the general kernel.
+    keys, p_j = exp(s_j) / (exp(sink) + sum exp(s_j)); None for the usual softmax.  Values of another width run on the
+    general kernel; the sink is one more term at the end of every kernel's sums.
 
     q: [T, nq*hd] view (row stride free, unit inner stride); out: contiguous
     [T, nq*hd]; caches [pages, nkv, page_size, hd]; positions / row_of_token int32
@@ -548,11 +549,11 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
     _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _i32(block_table, "block_table")
     if block_table.stride(1) != 1:
         raise KernelError("paged_attention: block table rows must be contiguous")
-    if batch is not None and _KERNEL_SET == "fast" and vd == hd and sink is None and fast_attention_supported(q, nq, nkv, hd):
+    if batch is not None and _KERNEL_SET == "fast" and vd == hd and fast_attention_supported(q, nq, nkv, hd):
         if batch.max_q_len > 1:
             prefill = paged_attention_prefill_tc if tc_attention_supported(q, hd, page_size) else paged_attention_prefill
             prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                    window, batch.max_q_len, skip_single=batch.num_single > 0)
+                    window, batch.max_q_len, skip_single=batch.num_single > 0, sink=sink)
         if batch.num_single > 0 and stream_decode_supported(batch.num_rows, page_size, nq // nkv):
             ctas = sm_count(q.device)
             slots = (ctas + batch.num_rows * nkv) * (nq // nkv)
@@ -560,7 +561,7 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
                 q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale, window,
                 batch.ws.get("attn_piece_o", (slots * hd,), torch.float32),
                 batch.ws.get("attn_piece_ml", (slots * 2,), torch.float32),
-                batch.ws.get_zeroed("attn_piece_counters", (batch.num_rows * nkv,), torch.int32), ctas)
+                batch.ws.get_zeroed("attn_piece_counters", (batch.num_rows * nkv,), torch.int32), ctas, sink=sink)
         elif batch.num_single > 0:
             splits = decode_splits(batch.num_rows, nkv, block_table.shape[1] * page_size, q.device)
             part_o = part_ml = counters = None
@@ -569,12 +570,17 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
                 part_ml = batch.ws.get("attn_part_ml", (batch.num_rows * nq * splits * 2,), torch.float32)
                 counters = batch.ws.get_zeroed("attn_split_counters", (batch.num_rows * nkv,), torch.int32)
             paged_attention_decode(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd,
-                                   page_size, scale, window, splits, part_o, part_ml, counters)
+                                   page_size, scale, window, splits, part_o, part_ml, counters, sink=sink)
         return
     _check(library().arle_paged_attention_plain(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _dt(q), _ptr(positions), _ptr(row_of_token),
         _ptr(block_table), block_table.stride(0), nq, nkv, hd, vd, page_size, float(scale),
         int(window) if window else 0, int(sink is not None), float(sink or 0.0), T, _stream()), "paged_attention")
+
+
+def _sink_arg(sink) -> float:
+    """The fast attention kernels take the sink's score as a number; minus infinity stands for no sink (its term is zero)."""
+    return float("-inf") if sink is None else float(sink)
 
 
 def fast_attention_supported(q, nq: int, nkv: int, hd: int) -> bool:
@@ -591,7 +597,7 @@ def tc_attention_supported(q, hd: int, page_size: int) -> bool:
 
 
 def paged_attention_prefill_tc(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                               window, max_q_len: int, skip_single: bool = False) -> None:
+                               window, max_q_len: int, skip_single: bool = False, sink: float = None) -> None:
     """Flash attention over the paged cache on the tcgen05 tensor cores (TMA-fed, scores
     and output in tensor memory) for rows with several queries."""
     R = kv_lens.numel()
@@ -601,7 +607,7 @@ def paged_attention_prefill_tc(q, out, k_cache, v_cache, q_indptr, kv_lens, bloc
     _check(library().arle_paged_attention_prefill_tc(
         _ptr(q), q.stride(0), q.shape[0], _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(q_indptr),
         _ptr(kv_lens), _ptr(block_table), block_table.stride(0), block_table.shape[1], nq, nkv, hd, page_size, float(scale),
-        int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _ptr(error_flag(q.device)), _stream()),
+        _sink_arg(sink), int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _ptr(error_flag(q.device)), _stream()),
         "paged_attention_prefill_tc")
 
 
@@ -624,7 +630,7 @@ def stream_decode_supported(rows: int, page_size: int, group: int = 1) -> bool:
 
 
 def paged_attention_decode_stream(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                                  window, piece_o, piece_ml, counters, ctas: int) -> None:
+                                  window, piece_o, piece_ml, counters, ctas: int, sink: float = None) -> None:
     """Attention of the rows that have exactly one query (others are skipped), as a
     resident grid of ``ctas`` CTAs that share the batch's 64-key tiles evenly.
     Scratch: piece_o float32 [(ctas + R*nkv) * (nq/nkv) * hd], piece_ml float32
@@ -644,7 +650,7 @@ def paged_attention_decode_stream(q, out, k_cache, v_cache, q_indptr, kv_lens, b
     _check(library().arle_paged_attention_decode_stream(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(q_indptr), _ptr(kv_lens),
         _ptr(block_table), block_table.stride(0), block_table.shape[1], _ptr(piece_o), _ptr(piece_ml), _ptr(counters),
-        nq, nkv, hd, page_size, float(scale), int(window) if window else 0, R, int(ctas), _ptr(error_flag(q.device)),
+        nq, nkv, hd, page_size, float(scale), _sink_arg(sink), int(window) if window else 0, R, int(ctas), _ptr(error_flag(q.device)),
         _stream()), "paged_attention_decode_stream")
 
 
@@ -703,7 +709,7 @@ def decode_attention_with_prep(qkv, out, k_cache, v_cache, slot_mapping, q_weigh
     _check(library().arle_paged_attention_decode_stream_prep(
         _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(batch.q_indptr),
         _ptr(batch.kv_lens), _ptr(block_table), block_table.stride(0), block_table.shape[1], _ptr(piece_o), _ptr(piece_ml),
-        _ptr(counters), nq, nkv, hd, page_size, float(scale), int(window) if window else 0, R, int(ctas), 1,
+        _ptr(counters), nq, nkv, hd, page_size, float(scale), _sink_arg(None), int(window) if window else 0, R, int(ctas), 1,
         _ptr(slot_mapping), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), _ptr(plan),
         _ptr(error_flag(qkv.device)), _stream()), "decode_attention_with_prep")
 
@@ -720,7 +726,7 @@ def decode_splits(rows: int, nkv: int, kv_bound: int, device=None) -> int:
 
 
 def paged_attention_decode(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                           window, splits: int, part_o=None, part_ml=None, counters=None) -> None:
+                           window, splits: int, part_o=None, part_ml=None, counters=None, sink: float = None) -> None:
     """Split-KV attention of the rows that have exactly one query (others are
     skipped).  q_indptr int32 [R+1], kv_lens int32 [R] (keys after this step).
     When splits > 1: part_o / part_ml are float32 scratch of R*nq*splits*hd and
@@ -735,11 +741,11 @@ def paged_attention_decode(q, out, k_cache, v_cache, q_indptr, kv_lens, block_ta
     _check(library().arle_paged_attention_decode(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_indptr), _ptr(kv_lens),
         _ptr(block_table), block_table.stride(0), _ptr(part_o), _ptr(part_ml), _ptr(counters), nq, nkv, hd, page_size,
-        float(scale), int(window) if window else 0, R, int(splits), _stream()), "paged_attention_decode")
+        float(scale), _sink_arg(sink), int(window) if window else 0, R, int(splits), _stream()), "paged_attention_decode")
 
 
 def paged_attention_prefill(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                            window, max_q_len: int, skip_single: bool = False) -> None:
+                            window, max_q_len: int, skip_single: bool = False, sink: float = None) -> None:
     """Flash-attention over the paged cache for rows with several queries (and,
     unless skip_single, for single-query rows too)."""
     R = kv_lens.numel()
@@ -747,7 +753,7 @@ def paged_attention_prefill(q, out, k_cache, v_cache, q_indptr, kv_lens, block_t
     _check(library().arle_paged_attention_prefill(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_indptr), _ptr(kv_lens),
         _ptr(block_table), block_table.stride(0), nq, nkv, hd, page_size, float(scale),
-        int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _stream()), "paged_attention_prefill")
+        _sink_arg(sink), int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _stream()), "paged_attention_prefill")
 
 
 # ------------------------------------------------------------------ activation
@@ -1058,21 +1064,22 @@ def dyt_norm(resid, delta, rows, weight, bias, alpha: float, out, write_resid: b
 def gemm_heads(x, w, out) -> None:
     """out[m, h, :] = x[m, h, :] . w[h]^T for every head h: x [M, heads, K], w [heads, N, K] contiguous, out [M, heads, N].
     x and out may be views into wider rows (any row stride and head stride, unit inner stride).  float32 sums; k ascending
-    in the general kernel, tensor-core tiles for bfloat16 rows on 16-byte boundaries (fast kernel set)."""
+    in the general kernel, tensor-core tiles for bfloat16 rows on 16-byte boundaries (fast kernel set).  ``out`` has x's
+    type, or is float32 (the sums as they are) for bfloat16 rows."""
     M, heads, K = x.shape
     N = w.shape[1]
     if (w.shape[0] != heads or w.shape[2] != K or tuple(out.shape) != (M, heads, N) or not w.is_contiguous()
-            or x.stride(2) != 1 or out.stride(2) != 1 or x.dtype != out.dtype):
+            or x.stride(2) != 1 or out.stride(2) != 1 or (x.dtype != out.dtype and out.dtype != torch.float32)):
         raise KernelError(f"gemm_heads: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     if x.dtype == torch.bfloat16 and w.dtype != torch.bfloat16:
         raise KernelError("gemm_heads: bfloat16 rows need bfloat16 matrices")
     if (_KERNEL_SET == "fast" and x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
         # the same sums on the tensor cores (tiles of 64 rows x 128 columns)
-        _check(library().arle_gemm_heads_mma(_ptr(x), _ptr(w), _ptr(out), M, N, K, heads, x.stride(0), K, out.stride(0), x.stride(1),
+        _check(library().arle_gemm_heads_mma(_ptr(x), _ptr(w), _ptr(out), _dt(out), M, N, K, heads, x.stride(0), K, out.stride(0), x.stride(1),
                                              N * K, out.stride(1), _stream()), "gemm_heads_mma")
         return
-    _check(library().arle_gemm_heads(_ptr(x), _ptr(w), _ptr(out), _dt(x), _dt(w), M, N, K, heads, x.stride(0), K, out.stride(0),
+    _check(library().arle_gemm_heads(_ptr(x), _ptr(w), _ptr(out), _dt(x), _dt(w), _dt(out), M, N, K, heads, x.stride(0), K, out.stride(0),
                                      x.stride(1), N * K, out.stride(1), _stream()), "gemm_heads")
 
 
@@ -1457,13 +1464,13 @@ def rglru_scan(z, u, y, bias_r, bias_i, lam, y_bias, c_decay: float, state, q_in
     """The real-gated linear recurrent unit over the tokens of every row of the step, from and into state[state_slots[r]]
     (its first ``width`` numbers): r = sigmoid(z_r + bias_r), i = sigmoid(z_i + bias_i), a = exp(-c_decay * r * softplus(lam)),
     S_t = a S_(t-1) + sqrt(1 - a^2) * i * u_t, out_t = S_t * gelu_tanh(y_t + y_bias).  z float32 [T, 2*width] contiguous, per
-    token and block of width/blocks channels the recurrence gates' sums, then the input gates'; u float32 [T, width]
-    contiguous; y, out [T, width] in the activation type (views of wider rows are fine); the rest float32 [width]."""
+    token and block of width/blocks channels the recurrence gates' sums, then the input gates'; u [T, width] contiguous
+    and y, out [T, width] (views of wider rows are fine) in the activation type; the rest float32 [width]."""
     T, width = u.shape
     R = state_slots.numel()
-    if (z.dtype != torch.float32 or tuple(z.shape) != (T, 2 * width) or not z.is_contiguous() or u.dtype != torch.float32
+    if (z.dtype != torch.float32 or tuple(z.shape) != (T, 2 * width) or not z.is_contiguous() or u.dtype != y.dtype
             or not u.is_contiguous() or width % blocks):
-        raise KernelError("rglru_scan: z float32 [T, 2*width] and u float32 [T, width], contiguous; width a multiple of blocks")
+        raise KernelError("rglru_scan: z float32 [T, 2*width] and u [T, width] in y's type, contiguous; width a multiple of blocks")
     if tuple(y.shape) != (T, width) or tuple(out.shape) != (T, width) or y.stride(1) != 1 or out.stride(1) != 1 or y.dtype != out.dtype:
         raise KernelError("rglru_scan: y and out must be [T, width] of one type with unit inner stride")
     for t_ in (bias_r, bias_i, lam) + ((y_bias,) if y_bias is not None else ()):

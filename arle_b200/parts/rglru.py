@@ -9,9 +9,9 @@ no activation).  u is cut into ``blocks`` equal parts; in part b, with square ma
     S_t = a S_(t-1) + sqrt(1 - a^2) * i * u_t          (S = 0 before the first token, which is no special case)
 
 and the output is W_o (S * y).  The state (S, float32, and the convolution's last taps - 1 inputs) lives in the request's
-state slot.  u, the gates, the decay and the recurrence are float32 in both precisions: the convolution writes float32
-and the block-diagonal product reads it.  W_y and W_x are one packed product; the two gate matrices of a block are
-one matrix [2 * bs, bs], so the gates' sums are one block-diagonal product.
+state slot.  The gates, the decay and the recurrence are float32 in both precisions: the block-diagonal product that
+forms the gates' sums reads u in the activation type and leaves its float32 sums as they are.  W_y and W_x are one packed
+product; the two gate matrices of a block are one matrix [2 * bs, bs], so the gates' sums are one block-diagonal product.
 """
 from __future__ import annotations
 
@@ -73,8 +73,7 @@ class RgLru(Mixer):
         self.w_yx = torch.cat([y.to(device=device, dtype=kept(y, x)), x.to(device=device, dtype=kept(y, x))], dim=0).contiguous()
         self.w_o = o.to(device=device, dtype=kept(o)).contiguous()
         ra, ri = tensors[self._name("ra")], tensors[self._name("ri")]
-        # the gates read float32 rows, so their matrices are kept as stored (a float32 product either way)
-        self.w_gates = torch.cat([ra, ri], dim=1).to(device=device).contiguous()                      # [blocks, 2 * bs, bs]
+        self.w_gates = torch.cat([ra, ri], dim=1).to(device=device, dtype=kept(ra, ri)).contiguous()     # [blocks, 2 * bs, bs]
         self.y_bias, self.x_bias, self.conv, self.conv_bias, self.lam = (
             tensors[self._name(n)].to(device=device, dtype=torch.float32).contiguous() for n in ("y_bias", "x_bias", "conv", "conv_bias", "lam"))
         self.ra_bias, self.ri_bias = (tensors[self._name(n)].to(device=device, dtype=torch.float32).reshape(-1).contiguous()
@@ -95,7 +94,7 @@ class RgLru(Mixer):
         T, W = x.shape[0], s.width
         yx = ctx.ws.get("lru_yx", (T, 2 * W), x.dtype)
         ops.gemm(x, self.w_yx, yx)
-        u = ctx.ws.get("lru_u", (T, W), torch.float32)
+        u = ctx.ws.get("lru_u", (T, W), x.dtype)
         ops.causal_conv(yx[:, W:], self.x_bias, self.conv, self.conv_bias, "none", state, W, ctx.q_indptr, ctx.row_of_token,
                         ctx.state_slots, u)
         z = ctx.ws.get("lru_z", (T, 2 * W), torch.float32)

@@ -19,6 +19,9 @@ single-GPU one: for --gpus above 1 it says so and exits with 2.
 beside as many Qwen3 layers of equal sizes, prefill and decode, with every kernel's time per layer.
 ``--design zuderax`` does the same for Zuderax layers (a latent attention, a matrix LSTM and a Mamba-2 layer in turn,
 every second feed-forward one of routed experts) beside Kolodra and Qwen3 layers of equal width.
+``--design lasupel`` does the same for Lasupel layers (an attention with a sliding window and a sink, an RG-LRU layer, an
+attention that reads the first one's keys and values, a gated delta rule layer, in turn; the first feed-forward of four
+dense, the others routed experts) beside Zuderax and Qwen3 layers of equal width.
 """
 import argparse
 import json
@@ -178,6 +181,34 @@ def zuderax_config(z, zz, L, window):
     return {"architecture": "Zuderax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": layers}
 
 
+# Mixer sizes for ``--design lasupel`` at the same widths: the attention's heads are the Qwen3 layer's (a window of half the
+# benchmark's context, a quarter of a head rotated), the RG-LRU is as wide as the model with gate blocks of 128 / 256
+# channels, the delta rule has states of 128 x 128 (half as many key heads as value heads), and the chosen experts together
+# are as wide as the dense feed-forward.
+LASUPEL_SIZES = {"0.6b": dict(lru_blocks=8, delta=(8, 4, 128, 128), experts=16, top=4, groups=4, keep=2),
+                 "8b": dict(lru_blocks=16, delta=(32, 16, 128, 128), experts=32, top=4, groups=4, keep=2)}
+
+
+def lasupel_config(z, ll, L, window):
+    ff = {"kind": "dense", "ff": z["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": z["ff"] // ll["top"], "limit": 7.0},
+              "router": {"experts": ll["experts"], "top": ll["top"], "groups": {"count": ll["groups"], "keep": ll["keep"]}}}
+    attn = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5, "mask": {"size": window},
+            "rot": {"base": 1e6, "dims": z["hd"] // 4}}
+    h, g, dk, dv = ll["delta"]
+    layers = []
+    for i in range(L):
+        if i % 4 == 0:
+            layers.append({"type": "attention", "mixer": dict(attn), "mlp": ff})
+        elif i % 4 == 1:
+            layers.append({"type": "rglru", "mixer": {"width": z["width"], "blocks": ll["lru_blocks"], "conv": 4}, "mlp": routed})
+        elif i % 4 == 2:
+            layers.append({"type": "attention", "mixer": dict(attn, kv_from=i - 2), "mlp": routed})
+        else:
+            layers.append({"type": "delta", "mixer": {"heads": h, "kv_heads": g, "dim": dk, "vdim": dv, "conv": 4}, "mlp": routed})
+    return {"architecture": "Lasupel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": layers}
+
+
 def design_table(args, torch, ops, pk) -> int:
     """``--design kolodra``: prefill and decode throughput of a few Kolodra layers beside the same number of Qwen3
     layers of equal width, heads and feed-forward, with the device time of every kernel of one step (profiler
@@ -187,7 +218,7 @@ def design_table(args, torch, ops, pk) -> int:
     from arle_b200.engine import ModelRunner, StepEntry, random_model
 
     dev = torch.device("cuda:0")
-    L, T, C = args.layers or (6 if args.design == "zuderax" else 4), args.prefill_tokens, args.context
+    L, T, C = args.layers or (6 if args.design == "zuderax" else (8 if args.design == "lasupel" else 4)), args.prefill_tokens, args.context
     gen = torch.Generator().manual_seed(1)
     out = {"design": args.design, "layers": L, "prefill_tokens": T, "context": C, "dtype": "bf16", "peaks": pk, "sizes": {}}
 
@@ -289,7 +320,13 @@ def design_table(args, torch, ops, pk) -> int:
         if args.design == "zuderax":
             out["sizes"][name]["mixers"] = ZUDERAX_SIZES[name]
             out["sizes"][name]["zuderax"] = measure(zuderax_config(z, ZUDERAX_SIZES[name], L, max(C // 2, 16)))
-        if not args.design_alone:
+        if args.design == "lasupel":
+            out["sizes"][name]["mixers"] = LASUPEL_SIZES[name]
+            out["sizes"][name]["lasupel"] = measure(lasupel_config(z, LASUPEL_SIZES[name], L, max(C // 2, 16)))
+            if not args.design_alone:
+                out["sizes"][name].update({"zuderax": measure(zuderax_config(z, ZUDERAX_SIZES[name], L, max(C // 2, 16))),
+                                           "qwen3": measure(qwen_config(z))})
+        elif not args.design_alone:
             out["sizes"][name].update({"kolodra": measure(kolodra_config(z)), "qwen3": measure(qwen_config(z))})
     print(json.dumps(out))
     return 0
@@ -317,8 +354,8 @@ def main() -> int:
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--no-kernel-times", action="store_true",
                     help="with --design: leave out the per-kernel times (they come from torch's profiler, which cannot run under another profiler)")
-    ap.add_argument("--design-alone", action="store_true", help="with --design zuderax: leave out the models it stands beside")
-    ap.add_argument("--design", default=None, choices=["kolodra", "zuderax"],
+    ap.add_argument("--design-alone", action="store_true", help="with --design zuderax or lasupel: leave out the models it stands beside")
+    ap.add_argument("--design", default=None, choices=["kolodra", "zuderax", "lasupel"],
                     help="instead of the default workload: a few layers of this design beside as many Qwen3 layers of equal "
                          "sizes, prefill and decode, with every kernel's time (uses --layers, --steps, --context, --prefill-tokens)")
     ap.add_argument("--timeline", action="store_true",

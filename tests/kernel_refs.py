@@ -495,7 +495,7 @@ def rglru_scan(z, u, y, bias_r, bias_i, lam, y_bias, c_decay, state, q_indptr, s
     ig = torch.sigmoid(zz[:, :, 1].reshape(T, width) + bias_i)
     log_a = -c_decay * rg * torch.nn.functional.softplus(lam)
     a = torch.exp(log_a)
-    b = torch.sqrt(-torch.expm1(2.0 * log_a)) * ig * u
+    b = torch.sqrt(-torch.expm1(2.0 * log_a)) * ig * u.to(F32)
     yy = y.to(F32) + (y_bias if y_bias is not None else 0.0)
     yy = 0.5 * yy * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (yy + 0.044715 * yy ** 3)))
     for r in range(state_slots.numel()):

@@ -189,7 +189,7 @@ def test_rglru_scan_kernel(dtype, width, blocks, lens):
     state = torch.randn(6, width + 9, generator=g)
     st_gpu, st_cpu = state.clone().to(DEV), state.clone()
     for call in range(2):
-        z, u = torch.randn(T, 2 * width, generator=g), torch.randn(T, width, generator=g)
+        z, u = torch.randn(T, 2 * width, generator=g), torch.randn(T, width, generator=g).to(dtype)
         y = torch.randn(T, width + 3, generator=g).to(dtype)[:, :width]
         out = torch.zeros(T, width, dtype=dtype)
         gpu_out = out.to(DEV)
@@ -198,6 +198,21 @@ def test_rglru_scan_kernel(dtype, width, blocks, lens):
         kernel_refs.rglru_scan(z, u, y, br, bi, lam, yb, 8.0, st_cpu, indptr, slots, out, blocks, max(lens))
         torch.testing.assert_close(gpu_out.float().cpu(), out.float(), **_tol(dtype))
         torch.testing.assert_close(st_gpu.cpu(), st_cpu, rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("kernels", ["fast", "plain"])
+@pytest.mark.parametrize("M,blocks,bs", [(1, 3, 16), (70, 4, 64), (9, 7, 8), (260, 2, 136), (5, 1, 40)])
+def test_gate_sums_of_bfloat16_rows_stay_float32(M, blocks, bs, kernels):
+    """The block-diagonal product behind the RG-LRU's gates reads bfloat16 rows and matrices and leaves its float32 sums
+    unrounded: against float64, far closer than a bfloat16 rounding of the result would be."""
+    g = torch.Generator().manual_seed(M + bs)
+    u = torch.randn(M, blocks * bs, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(blocks, 2 * bs, bs, generator=g) * bs ** -0.5).to(torch.bfloat16).to(DEV)
+    z = torch.zeros(M, 2 * blocks * bs, dtype=torch.float32, device=DEV)
+    with ops.use_kernel_set(kernels):
+        ops.gemm_heads(u.view(M, blocks, bs), w, z.view(M, blocks, 2 * bs))
+    want = torch.einsum("mhk,hnk->mhn", u.double().cpu().view(M, blocks, bs), w.double().cpu()).reshape(M, -1)
+    torch.testing.assert_close(z.double().cpu(), want, rtol=1e-5, atol=1e-5)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
@@ -255,6 +270,51 @@ def test_routing_and_clamped_experts_kernels():
             torch.testing.assert_close(a, c, **_tol(dtype))
         gate, up = gu[:, 0::2].double().clamp(max=1.3), gu[:, 1::2].double().clamp(-1.3, 1.3)
         torch.testing.assert_close(c.double(), gate * torch.sigmoid(1.702 * gate) * (up + 1), **_tol(dtype))
+
+
+@pytest.mark.parametrize("sink", [0.0, 1.5, -2.0])
+@pytest.mark.parametrize("nq,nkv,hd,ps,window", [(8, 2, 128, 16, None), (6, 3, 128, 16, 40), (4, 1, 64, 16, 33), (2, 2, 64, 32, 300)])
+def test_the_sink_in_the_tensor_core_attention_kernels(nq, nkv, hd, ps, window, sink):
+    """The sink is one more term at the end of every fast kernel's sums (prompts on mma.sync and on tcgen05, decoding with
+    split keys and streaming, with and without pieces to merge): each against the plain statement, which differs from the
+    usual softmax by far more than the tolerance."""
+    import math
+
+    from test_kernels_gpu import _fast_setup
+
+    scale = 2.0 / math.sqrt(hd)
+
+    def want(q, kc, vc, pos, rows, bt, sink_):
+        exp = torch.empty(q.shape[0], nq * hd, dtype=torch.bfloat16)
+        kernel_refs.paged_attention(q.cpu(), exp, kc.cpu(), vc.cpu(), pos.cpu(), rows.cpu(), bt.cpu(), nq, nkv, hd, ps, scale, window, sink=sink_)
+        return exp.float()
+
+    lens, q_lens = [130, 300, 128, 129, 9, 700], [130, 2, 128, 3, 1, 333]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=6)
+    exp = want(q, kc, vc, pos, rows, bt, sink)
+    assert (exp - want(q, kc, vc, pos, rows, bt, None)).abs().max() > 0.05
+    for fn in ([ops.paged_attention_prefill_tc] if hd == 128 else []) + [ops.paged_attention_prefill]:
+        out = torch.zeros(q.shape[0], nq * hd, dtype=torch.bfloat16, device=DEV)
+        fn(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, scale, window, max(q_lens), sink=sink)
+        ops.check_errors(DEV)
+        torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+    lens = [1, 63, 64, 65, 700, 2049, 17]
+    R = len(lens)
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, [1] * R, seed=3)
+    exp = want(q, kc, vc, pos, rows, bt, sink)
+    for splits in (1, 5):
+        out = torch.zeros(R, nq * hd, dtype=torch.bfloat16, device=DEV)
+        po, pml = torch.zeros(R * nq * splits * hd, device=DEV), torch.zeros(R * nq * splits * 2, device=DEV)
+        ops.paged_attention_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, scale, window, splits, po, pml,
+                                   torch.zeros(R * nkv, dtype=torch.int32, device=DEV), sink=sink)
+        torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+    for ctas in (3, 148):
+        slots = (ctas + R * nkv) * (nq // nkv)
+        out = torch.zeros(R, nq * hd, dtype=torch.bfloat16, device=DEV)
+        ops.paged_attention_decode_stream(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, scale, window, torch.zeros(slots * hd, device=DEV),
+                                          torch.zeros(slots * 2, device=DEV), torch.zeros(R * nkv, dtype=torch.int32, device=DEV), ctas, sink=sink)
+        ops.check_errors(DEV)
+        torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
 
 
 # ------------------------------------------------------------------ the engine

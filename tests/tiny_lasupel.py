@@ -59,8 +59,8 @@ TINY_L2 = model(157, 48, 2e-6, 1.0, [
     layer(delta(2, 1, 40, 24, 3), dense(64)),
     layer(rglru(56, 7, 2), moe(4, 2, 2, 2, 20, 1.0))])
 # L3: wider: head 64 and 128, gate blocks of 64, state columns past one block, aligned rows
-TINY_L3 = model(512, 256, 1e-6, 0.5, [
-    layer(attn(8, 2, 64, 64, 48, 0.125, 32, 50000.0), moe(16, 4, 4, 2, 64, 1.5)),
+TINY_L3 = model(512, 256, 3e-6, 0.75, [
+    layer(attn(8, 2, 64, 64, 48, 0.125, 32, 50000.0), moe(16, 4, 4, 2, 96, 1.25)),
     layer(rglru(256, 4, 4), dense(512)),
     layer(attn(8, 2, 64, 64, 20, 0.125, 32, 50000.0, kv_from=0), dense(256)),
     layer(delta(8, 4, 64, 128, 4), moe(8, 2, 1, 1, 128, 3.0)),
