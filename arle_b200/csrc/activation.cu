@@ -109,10 +109,44 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out
   }
 }
 
+// The same, four results a thread: inter and out_stride multiples of 4, both bases on boundaries of their accesses.
+template <typename T>
+__global__ void clamped_glu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter4, size_t total4, int out_stride, float limit,
+                                       float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter4;
+    const int i = (int)(idx - t * inter4) * 4;
+    float in[8], res[4];
+    load_vec<T, 8>(gu + t * 8 * inter4 + 2 * i, in);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float g = fminf(in[2 * j], limit);
+      const float u = fminf(fmaxf(in[2 * j + 1], -limit), limit);
+      res[j] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+    store_vec<T, 4>(out + t * (size_t)out_stride + i, res);
+  }
+}
+
 ARLE_API int arle_clamped_glu(const void* gu, void* out, int dtype, int num_tokens, int inter, int out_stride, float limit, float alpha,
                               cudaStream_t s) {
   if (num_tokens <= 0) return 0;
   if (inter <= 0 || out_stride < inter || !(limit > 0.f)) return ARLE_E_BADARG;
+  const size_t elem = dtype == 0 ? sizeof(float) : sizeof(__nv_bfloat16);
+  if ((dtype == 0 || dtype == 1) && inter % 4 == 0 && out_stride % 4 == 0 && vec_aligned<8>(gu, elem) && vec_aligned<4>(out, elem)) {
+    const size_t total4 = (size_t)num_tokens * (inter / 4);
+    size_t blocks = (total4 + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == 0)
+      launch_kernel(clamped_glu_vec_kernel<float>, dim3((int)blocks), dim3(256), 0, s, 1, (const float*)gu, (float*)out, inter / 4, total4,
+                    out_stride, limit, alpha);
+    else
+      launch_kernel(clamped_glu_vec_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, 1, (const __nv_bfloat16*)gu,
+                    (__nv_bfloat16*)out, inter / 4, total4, out_stride, limit, alpha);
+    return launch_status();
+  }
   const size_t total = (size_t)num_tokens * inter;
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;

@@ -41,6 +41,62 @@ __global__ void branch_norm_add_kernel(float* __restrict__ resid, const TA* __re
   }
 }
 
+// The same with four numbers a thread and access (hidden and branch_stride multiples of 4, bases on the accesses'
+// boundaries); the branch's numbers stay in shared memory between the two passes as above.
+template <typename TA>
+__global__ void branch_norm_add_vec_kernel(float* __restrict__ resid, const TA* __restrict__ branch, int branch_stride,
+                                           const float* __restrict__ weight, TA* __restrict__ copy, int hidden, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float xs[];
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  float* xr = resid + (size_t)t * hidden;
+  float inv = 0.f;
+  if (branch) {
+    const TA* br = branch + (size_t)t * branch_stride;
+    float ss = 0.f;
+    for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+      float x[4];
+      load_vec<TA, 4>(br + c, x);
+      store_vec<float, 4>(xs + c, x);
+      ss += x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    }
+    const float total = block_sum(ss, red);
+    inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  }
+  for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+    float x[4];
+    load_vec<float, 4>(xr + c, x);
+    if (branch) {
+      float b[4], w[4];
+      load_vec<float, 4>(xs + c, b);              // written by this thread
+      load_vec<float, 4>(weight + c, w);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] += b[i] * inv * w[i];
+      store_vec<float, 4>(xr + c, x);
+    }
+    if (copy) store_vec<TA, 4>(copy + (size_t)t * hidden + c, x);
+  }
+}
+
+template <typename TA>
+static int launch_branch_norm(float* resid, const void* branch, int branch_stride, const float* weight, void* copy, int num_tokens,
+                              int hidden, float eps, cudaStream_t s) {
+  const size_t smem = (size_t)hidden * sizeof(float);
+  const bool vec = hidden % 4 == 0 && branch_stride % 4 == 0 && vec_aligned<4>(resid, sizeof(float)) && vec_aligned<4>(weight, sizeof(float)) &&
+                   vec_aligned<4>(branch, sizeof(TA)) && vec_aligned<4>(copy, sizeof(TA));
+  auto kernel = vec ? branch_norm_add_vec_kernel<TA> : branch_norm_add_kernel<TA>;
+  if (smem > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int per = vec ? 4 : 1;
+  const int threads = hidden >= 2048 * per ? 512 : (hidden >= 512 * per ? 256 : 128);
+  launch_kernel(kernel, dim3(num_tokens), dim3(threads), smem, s, 1, resid, (const TA*)branch, branch_stride, weight, (TA*)copy, hidden, eps);
+  return launch_status();
+}
+
 // resid float32 [T, hidden] contiguous; branch [T, hidden] in the activation type (row stride given) or null;
 // weight float32 [hidden]; copy [T, hidden] contiguous in the activation type or null.
 ARLE_API int arle_branch_norm_add(float* resid, const void* branch, int branch_stride, const float* weight, void* copy, int dtype,
@@ -48,25 +104,8 @@ ARLE_API int arle_branch_norm_add(float* resid, const void* branch, int branch_s
   if (num_tokens <= 0) return 0;
   if (hidden <= 0 || (branch && !weight)) return ARLE_E_BADARG;
   if (!branch && !copy) return 0;
-  const size_t smem = (size_t)hidden * sizeof(float);
-  if (smem > 160 * 1024) return ARLE_E_UNSUPPORTED;
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  if (dtype == 0) {
-    if (smem > 40 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(branch_norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-    }
-    launch_kernel(branch_norm_add_kernel<float>, dim3(num_tokens), dim3(threads), smem, s, 1, resid, (const float*)branch, branch_stride,
-                  weight, (float*)copy, hidden, eps);
-  } else if (dtype == 1) {
-    if (smem > 40 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(branch_norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-    }
-    launch_kernel(branch_norm_add_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), smem, s, 1, resid, (const __nv_bfloat16*)branch,
-                  branch_stride, weight, (__nv_bfloat16*)copy, hidden, eps);
-  } else {
-    return ARLE_E_BADARG;
-  }
-  return launch_status();
+  if ((size_t)hidden * sizeof(float) > 160 * 1024) return ARLE_E_UNSUPPORTED;
+  if (dtype == 0) return launch_branch_norm<float>(resid, branch, branch_stride, weight, copy, num_tokens, hidden, eps, s);
+  if (dtype == 1) return launch_branch_norm<__nv_bfloat16>(resid, branch, branch_stride, weight, copy, num_tokens, hidden, eps, s);
+  return ARLE_E_BADARG;
 }

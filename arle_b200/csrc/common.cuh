@@ -30,6 +30,29 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
   return __float2bfloat16_rn(v);
 }
 
+// VEC consecutive numbers of type T as one aligned access (p on a VEC * sizeof(T) boundary; 16 bytes an instruction).
+template <typename T, int VEC> struct alignas(sizeof(T) * VEC) Pack { T e[VEC]; };
+
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(const T* p, float (&v)[VEC]) {
+  const Pack<T, VEC> pk = *reinterpret_cast<const Pack<T, VEC>*>(p);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) v[i] = to_f32(pk.e[i]);
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void store_vec(T* p, const float (&v)[VEC]) {
+  Pack<T, VEC> pk;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) pk.e[i] = from_f32<T>(v[i]);
+  *reinterpret_cast<Pack<T, VEC>*>(p) = pk;
+}
+
+template <int VEC>
+__host__ __device__ __forceinline__ bool vec_aligned(const void* p, size_t elem) {
+  return ((uintptr_t)p % (elem * VEC)) == 0;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

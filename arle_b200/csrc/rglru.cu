@@ -11,7 +11,8 @@
 //        S_t = a S_(t-1) + sqrt(1 - a^2) * i * u_t,   out = S_t * act(y_t + y_bias)   (act: the tanh form of gelu)
 //    all in float32; S lives in the request's state slot.  A thread holds one channel and `seg_len` consecutive tokens:
 //    it runs them from a zero state, the segments' (product of a, end state) pairs are chained in order through shared
-//    memory, and the tokens are run again from the true incoming state; 32 channels x up to 32 segments a block.
+//    memory, and the tokens are run again from the true incoming state; 32 channels x up to 32 segments a block, or 16
+//    channels x up to 64 segments for long rows of a narrow model.
 #include "common.cuh"
 using namespace arle;
 
@@ -93,24 +94,28 @@ ARLE_API int arle_causal_conv(const void* x, int dtype, int x_stride, const floa
 
 // ------------------------------------------------------------------------------------------------ the recurrence
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+// 0.5 z (1 + tanh(w)) with w = sqrt(2 / pi) (z + 0.044715 z^3), written as z / (1 + exp(-2 w)): the same function, one
+// exponential and one division.
 __device__ __forceinline__ float gelu_tanh_f32(float z) {
-  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.0f + expf(-1.5957691216057308f * (z + 0.044715f * z * z * z)));
 }
 
-constexpr int kLruChannels = 32;          // and up to 32 segments: 1,024 threads a block
+constexpr int kLruThreads = 1024;      // CH channels x up to 1,024 / CH segments a block
 constexpr int kLruMaxSeg = 8;          // tokens a thread holds at a time
 
-template <typename T>
-__global__ void __launch_bounds__(kLruChannels * 32) rglru_scan_kernel(const float* __restrict__ z, const T* __restrict__ u, const T* __restrict__ y, int y_stride,
+// CH: 32 channels a block (a warp's lanes); 16 channels and up to 64 segments for rows of more than 256 tokens when the
+// step's blocks are so few that twice as many still run at once (a single prompt of a narrow model).
+template <typename T, int CH>
+__global__ void __launch_bounds__(kLruThreads) rglru_scan_kernel(const float* __restrict__ z, const T* __restrict__ u, const T* __restrict__ y, int y_stride,
                                   const float* __restrict__ bias_r, const float* __restrict__ bias_i, const float* __restrict__ lam,
                                   const float* __restrict__ y_bias, float c_decay, float* __restrict__ state, long slot_stride,
                                   const int* __restrict__ q_indptr, const int* __restrict__ state_slots, T* __restrict__ out,
                                   int out_stride, int width, int bs) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float seg_a[32][kLruChannels + 1], seg_b[32][kLruChannels + 1];
+  __shared__ float seg_a[kLruThreads / CH][CH + 1], seg_b[kLruThreads / CH][CH + 1];
   const int r = blockIdx.y;
-  const int c = blockIdx.x * kLruChannels + threadIdx.x;
+  const int c = blockIdx.x * CH + threadIdx.x;
   const int seg = threadIdx.y, nseg = blockDim.y;
   const bool live = c < width;
   const int beg = q_indptr[r], end = q_indptr[r + 1];
@@ -135,7 +140,7 @@ __global__ void __launch_bounds__(kLruChannels * 32) rglru_scan_kernel(const flo
         const float rg = 1.0f / (1.0f + expf(-(zt[zr_at] + br)));
         const float ig = 1.0f / (1.0f + expf(-(zt[zi_at] + bi)));
         const float log_a = -c_decay * rg * sp_lam;
-        const float at = expf(log_a);
+        const float at = 1.0f + expm1f(log_a);      // rounded to nearest also next to 1, where a biased last bit would add up over a long row
         a[j] = at;
         b[j] = sqrtf(-expm1f(2.0f * log_a)) * ig * to_f32(u[(size_t)t * width + c]);      // sqrt(1 - a^2), exact near a = 1
       }
@@ -186,16 +191,24 @@ ARLE_API int arle_rglru_scan(const float* z, const void* u, const void* y, int d
                              int max_q_len, cudaStream_t s) {
   if (R <= 0) return 0;
   if (width <= 0 || blocks <= 0 || width % blocks || R > 65535) return ARLE_E_BADARG;
+  // 16 channels a block only where the row is long and twice the blocks still run at once
+  const int ch = max_q_len > 32 * kLruMaxSeg && (long)((width + 31) / 32) * R * 2 <= 148 ? 16 : 32;
   int nseg = 1;
-  while (nseg < 32 && nseg * kLruMaxSeg < max_q_len) nseg <<= 1;
-  dim3 grid((width + kLruChannels - 1) / kLruChannels, R), block(kLruChannels, nseg);
-  if (dtype == 0)
-    launch_kernel(rglru_scan_kernel<float>, dim3(grid), dim3(block), 0, s, 1, z, (const float*)u, (const float*)y, y_stride, bias_r, bias_i, lam, y_bias,
-                  c_decay, state, slot_stride, q_indptr, state_slots, (float*)out, out_stride, width, width / blocks);
+  while (nseg < kLruThreads / ch && nseg * kLruMaxSeg < max_q_len) nseg <<= 1;
+  dim3 grid((width + ch - 1) / ch, R), block(ch, nseg);
+#define ARLE_LRU(TT, CH) \
+  launch_kernel(rglru_scan_kernel<TT, CH>, dim3(grid), dim3(block), 0, s, 1, z, (const TT*)u, (const TT*)y, y_stride, bias_r, bias_i, lam, \
+                y_bias, c_decay, state, slot_stride, q_indptr, state_slots, (TT*)out, out_stride, width, width / blocks)
+  if (dtype == 0 && ch == 32)
+    ARLE_LRU(float, 32);
+  else if (dtype == 0)
+    ARLE_LRU(float, 16);
+  else if (dtype == 1 && ch == 32)
+    ARLE_LRU(__nv_bfloat16, 32);
   else if (dtype == 1)
-    launch_kernel(rglru_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(block), 0, s, 1, z, (const __nv_bfloat16*)u, (const __nv_bfloat16*)y, y_stride, bias_r, bias_i,
-                  lam, y_bias, c_decay, state, slot_stride, q_indptr, state_slots, (__nv_bfloat16*)out, out_stride, width, width / blocks);
+    ARLE_LRU(__nv_bfloat16, 16);
   else
     return ARLE_E_BADARG;
+#undef ARLE_LRU
   return launch_status();
 }

@@ -97,7 +97,7 @@ def _rows(g, starts, lens, ps, extra_pages=5):
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 def test_branch_norm_add_kernel(dtype):
     g = torch.Generator().manual_seed(0)
-    for H in (48, 100, 256, 4096):
+    for H in (48, 51, 100, 256, 4096):
         resid = torch.randn(7, H, generator=g) * 3
         branch = (torch.randn(7, H + 8, generator=g) * 5).to(dtype)[:, :H]                 # a view of wider rows
         w = torch.rand(H, generator=g) + 0.5
@@ -146,10 +146,13 @@ def test_preparation_and_attention_with_sink_and_value_width(dtype, nq, nkv, hd,
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("C,taps,out_f32", [(48, 3, True), (130, 4, False), (7, 2, True), (256, 5, False), (33, 1, True)])
-def test_causal_conv_kernel(dtype, C, taps, out_f32):
+@pytest.mark.parametrize("C,taps,out_f32,pad,at", [(48, 3, True, 5, 2), (130, 4, False, 5, 2), (7, 2, True, 5, 2), (256, 5, False, 5, 2),
+                                                     (33, 1, True, 5, 2), (48, 3, True, 16, 8), (256, 4, False, 24, 16), (1032, 2, False, 8, 0),
+                                                     (8, 1, True, 8, 8)])
+def test_causal_conv_kernel(dtype, C, taps, out_f32, pad, at):
     """Rows shorter than the taps reach back into the state; a second call continues from the state the first one left; an
-    input bias is added to the request's tokens and not to the zeros before them."""
+    input bias is added to the request's tokens and not to the zeros before them.  The channels are views into wider rows,
+    at odd places and on 16-byte boundaries."""
     g = torch.Generator().manual_seed(C)
     lens = [1, 2, 9, 1, 30]
     T = sum(lens)
@@ -163,10 +166,11 @@ def test_causal_conv_kernel(dtype, C, taps, out_f32):
     for act, in_bias, out_bias in (("none", ib, ob), ("silu", None, None), ("silu", ib, None)):
         st_gpu, st_cpu = state.clone().to(DEV), state.clone()
         for call in range(2):
-            x = torch.randn(T, C + 5, generator=g).to(dtype)[:, 2: 2 + C]
+            wide = torch.randn(T, C + pad, generator=g).to(dtype)
+            x = wide[:, at: at + C]
             out = torch.zeros(T, C, dtype=torch.float32 if out_f32 else dtype)
             gpu_out = out.to(DEV)
-            ops.causal_conv(x.to(DEV), in_bias.to(DEV) if in_bias is not None else None, w.to(DEV), out_bias.to(DEV) if out_bias is not None else None,
+            ops.causal_conv(wide.to(DEV)[:, at: at + C], in_bias.to(DEV) if in_bias is not None else None, w.to(DEV), out_bias.to(DEV) if out_bias is not None else None,
                             act, st_gpu, off, indptr.to(DEV), row.to(DEV), slots.to(DEV), gpu_out)
             kernel_refs.causal_conv(x, in_bias, w, out_bias, act, st_cpu, off, indptr, row, slots, out)
             torch.testing.assert_close(gpu_out.float().cpu(), out.float(), **_tol(dtype))
@@ -175,7 +179,7 @@ def test_causal_conv_kernel(dtype, C, taps, out_f32):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("width,blocks,lens", [(48, 3, [1, 5, 70]), (40, 1, [300, 1, 2]), (256, 4, [33, 1, 9, 1]), (56, 7, [1, 1, 1])])
+@pytest.mark.parametrize("width,blocks,lens", [(48, 3, [1, 5, 70]), (40, 1, [300, 1, 2]), (256, 4, [33, 1, 9, 1]), (56, 7, [1, 1, 1]), (72, 2, [256, 257, 700, 3])])
 def test_rglru_scan_kernel(dtype, width, blocks, lens):
     """Rows of unequal length from states in permuted slots; long rows run in segments whose states are chained; a second
     call continues.  Some decays are next to one (lam far below zero) so that a lost state would show."""
@@ -187,17 +191,17 @@ def test_rglru_scan_kernel(dtype, width, blocks, lens):
     lam[::3] = -9.0
     br, bi, yb = torch.randn(width, generator=g), torch.randn(width, generator=g), torch.randn(width, generator=g) * 0.2
     state = torch.randn(6, width + 9, generator=g)
-    st_gpu, st_cpu = state.clone().to(DEV), state.clone()
+    st_gpu, st_cpu = state.clone().to(DEV), state.double()                 # the statement runs in float64
     for call in range(2):
         z, u = torch.randn(T, 2 * width, generator=g), torch.randn(T, width, generator=g).to(dtype)
         y = torch.randn(T, width + 3, generator=g).to(dtype)[:, :width]
-        out = torch.zeros(T, width, dtype=dtype)
-        gpu_out = out.to(DEV)
+        out = torch.zeros(T, width, dtype=torch.float64)
+        gpu_out = torch.zeros(T, width, dtype=dtype, device=DEV)
         ops.rglru_scan(z.to(DEV), u.to(DEV), y.to(DEV), br.to(DEV), bi.to(DEV), lam.to(DEV), yb.to(DEV), 8.0, st_gpu, indptr.to(DEV),
                        slots.to(DEV), gpu_out, blocks, max(lens))
-        kernel_refs.rglru_scan(z, u, y, br, bi, lam, yb, 8.0, st_cpu, indptr, slots, out, blocks, max(lens))
-        torch.testing.assert_close(gpu_out.float().cpu(), out.float(), **_tol(dtype))
-        torch.testing.assert_close(st_gpu.cpu(), st_cpu, rtol=2e-5, atol=2e-5)
+        kernel_refs.rglru_scan(z.double(), u, y, br.double(), bi.double(), lam.double(), yb.double(), 8.0, st_cpu, indptr, slots, out, blocks, max(lens))
+        torch.testing.assert_close(gpu_out.double().cpu(), out, **_tol(dtype))
+        torch.testing.assert_close(st_gpu.double().cpu(), st_cpu, rtol=2e-5, atol=2e-5)
 
 
 @pytest.mark.parametrize("kernels", ["fast", "plain"])
@@ -217,12 +221,13 @@ def test_gate_sums_of_bfloat16_rows_stay_float32(M, blocks, bs, kernels):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("H,G,dim,vdim,lens", [(4, 2, 8, 12, [1, 5, 40]), (3, 3, 20, 8, [18, 1, 2]), (8, 4, 64, 128, [33, 1, 9]),
-                                               (2, 2, 160, 32, [1, 20, 1]), (2, 1, 300, 70, [3, 1, 17])])
+                                               (2, 2, 160, 32, [1, 20, 1]), (2, 1, 300, 70, [3, 1, 17]), (4, 2, 128, 128, [40, 1, 1]),
+                                               (40, 20, 32, 96, [1, 1, 19, 1, 1, 1]), (2, 1, 100, 33, [50])])
 def test_delta_rule_kernels(dtype, H, G, dim, vdim, lens):
     g = torch.Generator().manual_seed(H * 5 + dim)
     T = sum(lens)
     indptr = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
-    slots = torch.randperm(5, generator=g)[: len(lens)].to(torch.int32)
+    slots = torch.randperm(7, generator=g)[: len(lens)].to(torch.int32)
     pre = torch.randn(T, 2 * H + 3, generator=g)
     a_log, dtb = torch.randn(H, generator=g) * 0.5 - 1.0, torch.randn(H, generator=g)
     beta, decay = torch.zeros(T, H), torch.zeros(T, H)
@@ -230,7 +235,7 @@ def test_delta_rule_kernels(dtype, H, G, dim, vdim, lens):
     for (a, c) in res:
         torch.testing.assert_close(a, c, rtol=1e-5, atol=1e-6)
     beta, decay = res[0][1], res[1][1]
-    state = torch.randn(5, H * vdim * dim + 6, generator=g) * 0.3
+    state = torch.randn(7, H * vdim * dim + 6, generator=g) * 0.3
     st_gpu, st_cpu = state.clone().to(DEV), state.clone()
     for call in range(2):
         q, k = torch.randn(T, G * dim + 4, generator=g).to(dtype)[:, : G * dim], torch.randn(T, G * dim, generator=g).to(dtype)
@@ -264,12 +269,16 @@ def test_routing_and_clamped_experts_kernels():
         assert (ia.sort(-1).values == ic.sort(-1).values).all() and (ia.sort(-1).values.long() == want_i.sort(-1).values).all()
         torch.testing.assert_close(wa.sort(-1).values, want_w.float().sort(-1).values, rtol=1e-5, atol=1e-6)
     for dtype in DTYPES:
-        gu = (torch.randn(9, 2 * 40, generator=g) * 2).to(dtype)
-        out = torch.zeros(9, 44, dtype=dtype)[:, :40]
-        for (a, c) in _both("clamped_glu", [gu, out, 1.3, 1.702], [1]):
-            torch.testing.assert_close(a, c, **_tol(dtype))
-        gate, up = gu[:, 0::2].double().clamp(max=1.3), gu[:, 1::2].double().clamp(-1.3, 1.3)
-        torch.testing.assert_close(c.double(), gate * torch.sigmoid(1.702 * gate) * (up + 1), **_tol(dtype))
+        for inter, wide in ((40, 44), (37, 41), (256, 256)):          # four results a thread, and one
+            gu = (torch.randn(9, 2 * inter, generator=g) * 2).to(dtype)
+            out_gpu = torch.zeros(9, wide, dtype=dtype, device=DEV)
+            ops.clamped_glu(gu.to(DEV), out_gpu[:, :inter], 1.3, 1.702)
+            gate, up = gu[:, 0::2].double().clamp(max=1.3), gu[:, 1::2].double().clamp(-1.3, 1.3)
+            torch.testing.assert_close(out_gpu[:, :inter].double().cpu(), gate * torch.sigmoid(1.702 * gate) * (up + 1), **_tol(dtype))
+            assert float(out_gpu[:, inter:].abs().sum()) == 0.0
+            c = torch.zeros(9, inter, dtype=dtype)
+            kernel_refs.clamped_glu(gu, c, 1.3, 1.702)
+            torch.testing.assert_close(out_gpu[:, :inter].float().cpu(), c.float(), **_tol(dtype))
 
 
 @pytest.mark.parametrize("sink", [0.0, 1.5, -2.0])
