@@ -59,7 +59,7 @@ _SIGNATURES = {
     "arle_causal_conv": [_P, _I, _I, _P, _P, _P, _I, _P, ctypes.c_long, ctypes.c_long, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "arle_rglru_scan": [_P, _P, _P, _I, _I, _P, _P, _P, _P, _F, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_delta_gates": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
-    "arle_delta_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
+    "arle_delta_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "arle_clamped_glu": [_P, _P, _I, _I, _I, _I, _F, _F, _P],
     "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
     "arle_paged_attention_decode_stream": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
@@ -1525,5 +1525,5 @@ def delta_scan(q, k, v, beta, decay, state, q_indptr, state_slots, out, heads: i
     if q_indptr.numel() != R + 1:
         raise KernelError("delta_scan: q_indptr must have one entry more than state_slots")
     _check(library().arle_delta_scan(_ptr(q), _ptr(k), _ptr(v), _dt(q), q.stride(0), k.stride(0), v.stride(0), _ptr(beta), _ptr(decay),
-                                     _ptr(state), state.stride(0), _ptr(q_indptr), _ptr(state_slots), _ptr(out), R, heads, kq_heads,
+                                     _ptr(state), state.stride(0), _ptr(q_indptr), _ptr(state_slots), _ptr(out), T, R, heads, kq_heads,
                                      dim, vdim, float(q_scale), float(unit_eps), _stream()), "delta_scan")
