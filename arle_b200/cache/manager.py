@@ -69,8 +69,10 @@ class CacheGroup:
                        for heads, width in need.arrays()]
         # host block tables, one row per slot; logical page -> physical page, -1 = not held
         self.table = np.full((max_slots, max_pages_per_request), -1, dtype=np.int32)
-        self.first_held = np.zeros(max_slots, dtype=np.int64)     # first logical page still held
+        self.first_held = np.zeros(max_slots, dtype=np.int64)     # first logical page still held (past the kept first pages)
         self.num_logical = np.zeros(max_slots, dtype=np.int64)    # logical pages ever given to the slot
+        # pages that hold a request's first ``keep_first`` tokens stay for its life: logical pages [0, kept_pages)
+        self.kept_pages = -(-int(need.keep_first) // page_size) if need.window is not None and need.keep_first > 0 else 0
 
     def pages_for(self, slot: int, old_tokens: int, new_tokens: int) -> int:
         return max(0, -(-new_tokens // self.page_size) - int(self.num_logical[slot]))
@@ -138,8 +140,8 @@ class CacheManager:
         slot = self._slot_of.pop(rid)
         del self._tokens[rid]
         for g in self.groups:
-            lo, hi = int(g.first_held[slot]), int(g.num_logical[slot])
-            g.pool.free(int(p) for p in g.table[slot, lo:hi])
+            hi = int(g.num_logical[slot])
+            g.pool.free(int(p) for p in g.table[slot, :hi] if p >= 0)
             g.table[slot, :hi] = -1
             g.first_held[slot] = 0
             g.num_logical[slot] = 0
@@ -200,7 +202,8 @@ class CacheManager:
     def release_passed(self, rid) -> int:
         """Give back the pages of window groups that no later query of rid can see:
         a query at position p >= tokens sees keys >= p - window + 1, so a page whose
-        last token lies before tokens - window + 1 is done.  Returns pages freed."""
+        last token lies before tokens - window + 1 is done; the pages of the first tokens
+        that the group's need keeps visible stay.  Returns pages freed."""
         slot, n = self._slot_of[rid], self._tokens[rid]
         freed = 0
         for g in self.groups:
@@ -209,7 +212,7 @@ class CacheManager:
                 continue
             first_needed_token = max(0, n - w + 1)
             upto = min(first_needed_token // g.page_size, int(g.num_logical[slot]))
-            lo = int(g.first_held[slot])
+            lo = max(int(g.first_held[slot]), min(g.kept_pages, int(g.num_logical[slot])))
             if upto > lo:
                 g.pool.free(int(p) for p in g.table[slot, lo:upto])
                 g.table[slot, lo:upto] = -1
@@ -280,7 +283,8 @@ class CacheManager:
                     raise AssertionError(f"group {gi}: free slot {s} still lists pages")
                 held.extend(int(p) for p in live)
                 lo, hi = int(g.first_held[s]), int(g.num_logical[s])
-                if (row[lo:hi] < 0).any() or (row[:lo] >= 0).any() or (row[hi:] >= 0).any():
+                kp = min(g.kept_pages, hi)
+                if (row[lo:hi] < 0).any() or (row[kp:lo] >= 0).any() or (row[:min(kp, lo)] < 0).any() or (row[hi:] >= 0).any():
                     raise AssertionError(f"group {gi}: slot {s} table does not match its bounds")
             if len(held) != len(set(held)):
                 raise AssertionError(f"group {gi}: a page is held twice")

@@ -27,7 +27,7 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, int q_row_
                                              const int* __restrict__ row_of_token,
                                              const int* __restrict__ block_table, int bt_stride, int nq,
                                              int nkv, int hd, int vd, int page_size, float scale, int window, int has_sink,
-                                             float sink_logit) {
+                                             float sink_logit, int keep_first, float softcap) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float qs[256];
@@ -39,6 +39,8 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, int q_row_
   const int pos = positions[t];
   const int* bt = block_table + (size_t)row_of_token[t] * bt_stride;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int ka = min(keep_first, lo);                // kept first keys outside the window
+  const int nvis = ka + pos - lo + 1;                // visible keys: index i is key i (i < ka) or key lo + i - ka
 
   const T* qp = q + (size_t)t * q_row_stride + (size_t)h * hd;
   for (int e = threadIdx.x; e < hd; e += blockDim.x) qs[e] = to_f32(qp[e]) * scale;
@@ -51,28 +53,29 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, int q_row_
 
   const size_t page_stride = (size_t)nkv * page_size * hd;
   const size_t vpage_stride = (size_t)nkv * page_size * vd;
-  for (int j0 = lo + w * 32; j0 <= pos; j0 += kAttnWarps * 32) {
-    const int j = j0 + lane;
+  for (int i0 = w * 32; i0 < nvis; i0 += kAttnWarps * 32) {
+    const int iv = i0 + lane;
+    const int j = iv < ka ? iv : lo + iv - ka;
     float sc = -INFINITY;
-    if (j <= pos) {
+    if (iv < nvis) {
       const int page = bt[j / page_size];
       const T* kp = k_cache + (size_t)page * page_stride + ((size_t)kvh * page_size + j % page_size) * hd;
       float d = 0.f;
       for (int e = 0; e < hd; ++e) d = fmaf(qs[e], to_f32(kp[e]), d);
-      sc = d;
+      sc = softcap > 0.f ? softcap * tanhf(d / softcap) : d;
     }
     const float mt = warp_max(sc);
     const float m_new = fmaxf(m, mt);
-    const float p = j <= pos ? expf(sc - m_new) : 0.f;
+    const float p = iv < nvis ? expf(sc - m_new) : 0.f;
     const float corr = expf(m - m_new);
     l = l * corr + warp_sum(p);
 #pragma unroll
     for (int i = 0; i < kAttnMaxD; ++i) acc[i] *= corr;
     m = m_new;
-    const int nvalid = min(32, pos - j0 + 1);
+    const int nvalid = min(32, nvis - i0);
     for (int jj = 0; jj < nvalid; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const int jk = j0 + jj;
+      const int jk = i0 + jj < ka ? i0 + jj : lo + i0 + jj - ka;
       const int page = bt[jk / page_size];
       const T* vp = v_cache + (size_t)page * vpage_stride + ((size_t)kvh * page_size + jk % page_size) * vd;
 #pragma unroll
@@ -111,21 +114,22 @@ ARLE_API int arle_paged_attention_plain(const void* q, int q_row_stride, void* o
                                         const void* v_cache, int dtype, const int* positions,
                                         const int* row_of_token, const int* block_table, int bt_stride,
                                         int nq, int nkv, int hd, int vd, int page_size, float scale, int window,
-                                        int has_sink, float sink_logit, int num_tokens, cudaStream_t s) {
+                                        int has_sink, float sink_logit, int keep_first, float softcap, int num_tokens, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
   if (vd <= 0 || vd > 256) return ARLE_E_UNSUPPORTED;
   if (hd <= 0 || hd > 256 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0) return ARLE_E_UNSUPPORTED;
   if (nq > 65535) return ARLE_E_UNSUPPORTED;
+  if (keep_first < 0 || softcap < 0.f) return ARLE_E_BADARG;
   dim3 grid(num_tokens, nq);
   if (dtype == 0)
     launch_kernel(paged_attention_plain_kernel<float>, dim3(grid), dim3(kAttnWarps * 32), 0, s, 1, 
         (const float*)q, q_row_stride, (float*)out, (const float*)k_cache, (const float*)v_cache, positions,
-        row_of_token, block_table, bt_stride, nq, nkv, hd, vd, page_size, scale, window, has_sink, sink_logit);
+        row_of_token, block_table, bt_stride, nq, nkv, hd, vd, page_size, scale, window, has_sink, sink_logit, keep_first, softcap);
   else if (dtype == 1)
     launch_kernel(paged_attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(kAttnWarps * 32), 0, s, 1, 
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
         (const __nv_bfloat16*)v_cache, positions, row_of_token, block_table, bt_stride, nq, nkv, hd, vd,
-        page_size, scale, window, has_sink, sink_logit);
+        page_size, scale, window, has_sink, sink_logit, keep_first, softcap);
   else
     return ARLE_E_BADARG;
   return launch_status();

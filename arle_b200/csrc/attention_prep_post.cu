@@ -8,6 +8,8 @@
 //           x <- x / sqrt(mean(x^2) + eps) (* weight), store in place
 //   k head: the same, stored into k_cache at the token's slot
 //   v head: copied into v_cache at the token's slot
+// With norm_first the norm (and its weight) comes BEFORE the rotation instead: x <- x / sqrt(mean(x^2) + eps) * weight, then
+// the first rotary_dim numbers turn.
 // Everything between load and store is float32; the angle is evaluated with sincosf in float32.
 // Cache layout: keys [page][kv_head][slot_in_page][hd], values [page][kv_head][slot_in_page][vd]; slot_mapping[t] is
 // page * page_size + slot_in_page, negative = do not store.  nkv = 0: the rows hold q only.
@@ -22,7 +24,7 @@ __global__ void attention_prep_post_kernel(T* __restrict__ qkv, int row_stride, 
                                            const int* __restrict__ slot_mapping, const float* __restrict__ q_weight,
                                            const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq,
                                            int rotary_dim, T* __restrict__ k_cache, T* __restrict__ v_cache, int nq, int nkv, int hd,
-                                           int vd, int page_size, int num_tokens) {
+                                           int vd, int page_size, int num_tokens, int norm_first) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float bufs[kPostWarps][kPostMaxHead];
@@ -53,6 +55,15 @@ __global__ void attention_prep_post_kernel(T* __restrict__ qkv, int row_stride, 
   float* buf = bufs[w];
   for (int e = lane; e < hd; e += 32) buf[e] = to_f32(src[e]);
   __syncwarp();
+  const float* wt = kind == 0 ? q_weight : k_weight;
+  if (norm_first && eps >= 0.f) {
+    float s0 = 0.f;
+    for (int e = lane; e < hd; e += 32) s0 += buf[e] * buf[e];
+    s0 = warp_sum(s0);
+    const float inv0 = 1.0f / sqrtf(s0 / (float)hd + eps);
+    for (int e = lane; e < hd; e += 32) buf[e] = buf[e] * inv0 * (wt ? wt[e] : 1.0f);
+    __syncwarp();
+  }
   const float pos = (float)positions[t];
   const int half = rotary_dim >> 1;
   float ss = 0.f;
@@ -75,8 +86,8 @@ __global__ void attention_prep_post_kernel(T* __restrict__ qkv, int row_stride, 
     ss += x * x;
   }
   ss = warp_sum(ss);
-  const float inv = eps >= 0.f ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
-  const float* wt = kind == 0 ? q_weight : k_weight;
+  const float inv = (eps >= 0.f && !norm_first) ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
+  if (norm_first) wt = nullptr;
 #pragma unroll
   for (int i = 0; i < kPostMaxHead / 32; ++i) {
     const int e = lane + 32 * i;
@@ -94,7 +105,7 @@ __global__ void attention_prep_post_kernel(T* __restrict__ qkv, int row_stride, 
 ARLE_API int arle_attention_prep_post(void* qkv, int dtype, int row_stride, const int* positions, const int* slot_mapping,
                                       const float* q_weight, const float* k_weight, float eps, const float* inv_freq, int rotary_dim,
                                       void* k_cache, void* v_cache, int nq, int nkv, int hd, int vd, int page_size, int num_tokens,
-                                      cudaStream_t s) {
+                                      int norm_first, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
   if (hd <= 0 || hd > kPostMaxHead || vd <= 0 || nq <= 0 || nkv < 0 || page_size <= 0) return ARLE_E_UNSUPPORTED;
   if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > hd || (rotary_dim && !inv_freq)) return ARLE_E_BADARG;
@@ -105,11 +116,11 @@ ARLE_API int arle_attention_prep_post(void* qkv, int dtype, int row_stride, cons
   if (dtype == 0)
     launch_kernel(attention_prep_post_kernel<float>, dim3((unsigned)blocks), dim3(kPostWarps * 32), 0, s, 1, (float*)qkv, row_stride,
                   positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, (float*)k_cache, (float*)v_cache, nq, nkv, hd,
-                  vd, page_size, num_tokens);
+                  vd, page_size, num_tokens, norm_first);
   else if (dtype == 1)
     launch_kernel(attention_prep_post_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(kPostWarps * 32), 0, s, 1, (__nv_bfloat16*)qkv,
                   row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, (__nv_bfloat16*)k_cache,
-                  (__nv_bfloat16*)v_cache, nq, nkv, hd, vd, page_size, num_tokens);
+                  (__nv_bfloat16*)v_cache, nq, nkv, hd, vd, page_size, num_tokens, norm_first);
   else
     return ARLE_E_BADARG;
   return launch_status();

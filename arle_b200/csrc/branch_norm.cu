@@ -109,3 +109,86 @@ ARLE_API int arle_branch_norm_add(float* resid, const void* branch, int branch_s
   if (dtype == 1) return launch_branch_norm<__nv_bfloat16>(resid, branch, branch_stride, weight, copy, num_tokens, hidden, eps, s);
   return ARLE_E_BADARG;
 }
+
+// The same sum followed at once by the NEXT sublayer's norm, for blocks that norm a sublayer's input and its output:
+//
+//     resid[t, :] += branch[t, :] * rsqrt(mean(branch[t, :]^2) + eps) * weight          (float32)
+//     out[t, :]    = resid[t, :] * rsqrt(mean(resid[t, :]^2) + next_eps) * next_weight   (activation type)
+//
+// One pass over the residual instead of two kernels with a round trip between them.  A thread meets the same numbers
+// in all three loops, so the row in shared memory needs no barrier of its own.
+template <typename TA, int VEC>
+__global__ void branch_norm_add_norm_kernel(float* __restrict__ resid, const TA* __restrict__ branch, int branch_stride,
+                                            const float* __restrict__ weight, const float* __restrict__ next_weight, TA* __restrict__ out,
+                                            int hidden, float eps, float next_eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float xs[];
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  float* xr = resid + (size_t)t * hidden;
+  const TA* br = branch + (size_t)t * branch_stride;
+  float ss = 0.f;
+  for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
+    float x[VEC];
+    load_vec<TA, VEC>(br + c, x);
+    store_vec<float, VEC>(xs + c, x);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) ss += x[i] * x[i];
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)hidden + eps);
+  ss = 0.f;
+  for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
+    float x[VEC], b[VEC], w[VEC];
+    load_vec<float, VEC>(xr + c, x);
+    load_vec<float, VEC>(xs + c, b);
+    load_vec<float, VEC>(weight + c, w);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      x[i] += b[i] * inv * w[i];
+      ss += x[i] * x[i];
+    }
+    store_vec<float, VEC>(xr + c, x);
+    store_vec<float, VEC>(xs + c, x);
+  }
+  const float inv2 = 1.0f / sqrtf(block_sum(ss, red) / (float)hidden + next_eps);
+  for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
+    float x[VEC], w[VEC];
+    load_vec<float, VEC>(xs + c, x);
+    load_vec<float, VEC>(next_weight + c, w);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) x[i] = x[i] * inv2 * w[i];
+    store_vec<TA, VEC>(out + (size_t)t * hidden + c, x);
+  }
+}
+
+template <typename TA>
+static int launch_branch_norm_norm(float* resid, const void* branch, int branch_stride, const float* weight, const float* next_weight,
+                                   void* out, int num_tokens, int hidden, float eps, float next_eps, cudaStream_t s) {
+  const size_t smem = (size_t)hidden * sizeof(float);
+  const bool vec = hidden % 4 == 0 && branch_stride % 4 == 0 && vec_aligned<4>(resid, sizeof(float)) && vec_aligned<4>(weight, sizeof(float)) &&
+                   vec_aligned<4>(next_weight, sizeof(float)) && vec_aligned<4>(branch, sizeof(TA)) && vec_aligned<4>(out, sizeof(TA));
+  auto kernel = vec ? branch_norm_add_norm_kernel<TA, 4> : branch_norm_add_norm_kernel<TA, 1>;
+  if (smem > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int per = vec ? 4 : 1;
+  const int threads = hidden >= 2048 * per ? 512 : (hidden >= 512 * per ? 256 : 128);
+  launch_kernel(kernel, dim3(num_tokens), dim3(threads), smem, s, 1, resid, (const TA*)branch, branch_stride, weight, next_weight, (TA*)out,
+                hidden, eps, next_eps);
+  return launch_status();
+}
+
+// resid float32 [T, hidden] contiguous; branch [T, hidden] in the activation type (row stride given); weight, next_weight float32
+// [hidden]; out [T, hidden] contiguous in the activation type.
+ARLE_API int arle_branch_norm_add_norm(float* resid, const void* branch, int branch_stride, const float* weight, const float* next_weight,
+                                       void* out, int dtype, int num_tokens, int hidden, float eps, float next_eps, cudaStream_t s) {
+  if (num_tokens <= 0) return 0;
+  if (hidden <= 0 || !branch || !weight || !next_weight || !out) return ARLE_E_BADARG;
+  if ((size_t)hidden * sizeof(float) > 160 * 1024) return ARLE_E_UNSUPPORTED;
+  if (dtype == 0) return launch_branch_norm_norm<float>(resid, branch, branch_stride, weight, next_weight, out, num_tokens, hidden, eps, next_eps, s);
+  if (dtype == 1)
+    return launch_branch_norm_norm<__nv_bfloat16>(resid, branch, branch_stride, weight, next_weight, out, num_tokens, hidden, eps, next_eps, s);
+  return ARLE_E_BADARG;
+}

@@ -16,7 +16,7 @@
 //    q, k, alpha and v are staged in shared memory a chunk of tokens at a time, and o_t[j] is the sum
 //    over the column's lanes.  The order of every sum depends on (dim, vdim) only: a token's result
 //    does not depend on how the prompt was cut or on what else is in the batch.
-//  * gla_out: per head, o / sqrt(mean(o^2) + eps) * weight (shared by the heads), times silu(gate),
+//  * gla_out: per head, o / sqrt(mean(o^2) + eps) * weight (shared by the heads), times silu(gate) (or sigmoid(gate)),
 //    times a constant, rounded once into the activation type (a row of a wider buffer may be given).
 #include "common.cuh"
 using namespace arle;
@@ -279,7 +279,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float
 template <typename T, bool VEC4>
 __global__ void gla_out_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
                                const float* __restrict__ weight, float eps, float scale, T* __restrict__ out,
-                               int out_stride, int heads, int vdim, long long units) {
+                               int out_stride, int heads, int vdim, long long units, int sigmoid_gate) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -307,8 +307,13 @@ __global__ void gla_out_kernel(const float* __restrict__ o, const T* __restrict_
       }
       if (gp) {
         const float4 g = widen4(load_raw4(gp + e));
-        y[0] *= g.x / (1.0f + expf(-g.x)), y[1] *= g.y / (1.0f + expf(-g.y));
-        y[2] *= g.z / (1.0f + expf(-g.z)), y[3] *= g.w / (1.0f + expf(-g.w));
+        if (sigmoid_gate) {
+          y[0] *= 1.0f / (1.0f + expf(-g.x)), y[1] *= 1.0f / (1.0f + expf(-g.y));
+          y[2] *= 1.0f / (1.0f + expf(-g.z)), y[3] *= 1.0f / (1.0f + expf(-g.w));
+        } else {
+          y[0] *= g.x / (1.0f + expf(-g.x)), y[1] *= g.y / (1.0f + expf(-g.y));
+          y[2] *= g.z / (1.0f + expf(-g.z)), y[3] *= g.w / (1.0f + expf(-g.w));
+        }
       }
       store4(op + e, y[0] * scale, y[1] * scale, y[2] * scale, y[3] * scale);
     }
@@ -321,7 +326,7 @@ __global__ void gla_out_kernel(const float* __restrict__ o, const T* __restrict_
       if (weight) y *= weight[e];
       if (gate) {
         const float g = to_f32(gate[(size_t)t * gate_stride + (size_t)h * vdim + e]);
-        y *= g / (1.0f + expf(-g));
+        y *= (sigmoid_gate ? 1.0f : g) / (1.0f + expf(-g));
       }
       out[(size_t)t * out_stride + (size_t)h * vdim + e] = from_f32<T>(y * scale);
     }
@@ -402,7 +407,7 @@ ARLE_API int arle_gla_scan(const void* q, const void* k, const void* v, int dtyp
 }
 
 ARLE_API int arle_gla_out(const float* o, const void* gate, int dtype, int gate_stride, const float* weight, float eps,
-                          float scale, void* out, int out_stride, int num_tokens, int heads, int vdim, cudaStream_t s) {
+                          float scale, void* out, int out_stride, int num_tokens, int heads, int vdim, int sigmoid_gate, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
   if (heads <= 0 || vdim <= 0) return ARLE_E_BADARG;
   const long long units = (long long)num_tokens * heads;
@@ -415,11 +420,11 @@ ARLE_API int arle_gla_out(const float* o, const void* gate, int dtype, int gate_
   if (dtype == 0) {
     auto kern = vec ? gla_out_kernel<float, true> : gla_out_kernel<float, false>;
     launch_kernel(kern, dim3((unsigned)blocks), dim3(warps * 32), 0, s, 1, o, (const float*)gate, gate_stride, weight, eps, scale,
-                  (float*)out, out_stride, heads, vdim, units);
+                  (float*)out, out_stride, heads, vdim, units, sigmoid_gate);
   } else if (dtype == 1) {
     auto kern = vec ? gla_out_kernel<__nv_bfloat16, true> : gla_out_kernel<__nv_bfloat16, false>;
     launch_kernel(kern, dim3((unsigned)blocks), dim3(warps * 32), 0, s, 1, o, (const __nv_bfloat16*)gate, gate_stride, weight, eps,
-                  scale, (__nv_bfloat16*)out, out_stride, heads, vdim, units);
+                  scale, (__nv_bfloat16*)out, out_stride, heads, vdim, units, sigmoid_gate);
   } else {
     return ARLE_E_BADARG;
   }

@@ -5,7 +5,8 @@
 //    score when a group is a single expert), only experts of the `keep` best groups can be chosen (the others count as
 //    minus infinity); the `top` largest choice scores are chosen and weighted with s * scale (no renormalisation).
 //    Ties go to the lower index.  One thread per token, everything float32.  `mode` bit 0: the scores are a softmax
-//    over all experts instead of sigmoids; bit 1: a group's score is its largest choice score alone.
+//    over all experts instead of sigmoids; bit 1: a group's score is its largest choice score alone; bit 2: the sums z
+//    themselves are the choice scores and the weights are the softmax over the chosen sums alone (times scale).
 //  * moe_plan: sorts the step's (token, choice) pairs by expert (counts, offsets, a place for every pair) and lists
 //    the tiles of 64 places that the grouped product runs, one block of 1,024 threads; nothing goes through the host,
 //    so the step can be captured in a graph.  The order of the pairs inside an expert's run is whatever the
@@ -39,7 +40,7 @@ __global__ void moe_select_kernel(const float* __restrict__ z, int z_stride, con
     for (int e = 0; e < E; ++e) zsum += expf(zr[e] - zmax);
   }
   for (int e = 0; e < E; ++e)
-    ch[e] = ((mode & 1) ? expf(zr[e] - zmax) / zsum : 1.0f / (1.0f + expf(-zr[e]))) + (correction ? correction[e] : 0.f);
+    ch[e] = ((mode & 4) ? zr[e] : (mode & 1) ? expf(zr[e] - zmax) / zsum : 1.0f / (1.0f + expf(-zr[e]))) + (correction ? correction[e] : 0.f);
   const int per = E / groups;
   for (int g = 0; g < groups; ++g) {
     float b1 = -INFINITY, b2 = -INFINITY;
@@ -84,7 +85,14 @@ __global__ void moe_select_kernel(const float* __restrict__ z, int z_stride, con
     }
     ch[bi] = INFINITY;                                  // taken
     ids[(size_t)t * top + it] = bi;
-    wts[(size_t)t * top + it] = (mode & 1) ? scale * (expf(zr[bi] - zmax) / zsum) : scale / (1.0f + expf(-zr[bi]));
+    wts[(size_t)t * top + it] = (mode & 4) ? zr[bi] : (mode & 1) ? scale * (expf(zr[bi] - zmax) / zsum) : scale / (1.0f + expf(-zr[bi]));
+  }
+  if (mode & 4) {                                       // softmax over the chosen sums, in choice order
+    float* wr = wts + (size_t)t * top;
+    float cm = -INFINITY, cs = 0.f;
+    for (int it = 0; it < top; ++it) cm = fmaxf(cm, wr[it]);
+    for (int it = 0; it < top; ++it) cs += expf(wr[it] - cm);
+    for (int it = 0; it < top; ++it) wr[it] = scale * (expf(wr[it] - cm) / cs);
   }
 }
 

@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int q_stride, int k_stride, int v_stride,
     const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ state, long slot_stride,
     const int* __restrict__ q_indptr, const int* __restrict__ state_slots, float* __restrict__ out, int H, int kq_heads,
-    int dim, int vdim, int ones_col, float q_scale, int lpc) {
+    int dim, int vdim, int ones_col, float q_scale, int lpc, int ab_stride, int act) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float sm[];
@@ -64,16 +64,23 @@ __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
     for (int idx = threadIdx.x; idx < n * dpad; idx += kScanThreads) {
       const int tt = idx / dpad, e = idx - tt * dpad;
       const bool in = e < dim;
-      qs[idx] = in ? to_f32(q[(size_t)(t0 + tt) * q_stride + (size_t)g * dim + e]) * q_scale : 0.f;
-      ksm[idx] = in ? to_f32(k[(size_t)(t0 + tt) * k_stride + (size_t)g * dim + e]) : 0.f;
+      float qv = in ? to_f32(q[(size_t)(t0 + tt) * q_stride + (size_t)g * dim + e]) : 0.f;
+      float kv = in ? to_f32(k[(size_t)(t0 + tt) * k_stride + (size_t)g * dim + e]) : 0.f;
+      if (act) {
+        qv = qv / (1.0f + expf(-qv));
+        kv = kv / (1.0f + expf(-kv));
+      }
+      qs[idx] = qv * q_scale;
+      ksm[idx] = kv;
     }
     for (int idx = threadIdx.x; idx < n * cpb; idx += kScanThreads) {
       const int tt = idx / cpb, cc = idx - tt * cpb;
       const int c = c0 + cc;
-      const float vv = c < vdim ? to_f32(v[(size_t)(t0 + tt) * v_stride + (size_t)h * vdim + c]) : (c == vdim && ones_col ? 1.f : 0.f);
-      vs[idx] = b[(size_t)(t0 + tt) * H + h] * vv;
+      float vv = c < vdim ? to_f32(v[(size_t)(t0 + tt) * v_stride + (size_t)h * vdim + c]) : (c == vdim && ones_col ? 1.f : 0.f);
+      if (act && c < vdim) vv = vv / (1.0f + expf(-vv));
+      vs[idx] = b ? b[(size_t)(t0 + tt) * ab_stride + h] * vv : vv;
     }
-    if (threadIdx.x < n) as[threadIdx.x] = a[(size_t)(t0 + threadIdx.x) * H + h];
+    if (threadIdx.x < n) as[threadIdx.x] = a[(size_t)(t0 + threadIdx.x) * ab_stride + h];
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
       const float at = as[tt];
@@ -122,7 +129,7 @@ __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
 template <typename T, int EPL, int CPT>
 static int launch_scan_as(const void* q, const void* k, const void* v, int q_stride, int k_stride, int v_stride, const float* a,
                           const float* b, float* state, long slot_stride, const int* q_indptr, const int* state_slots, float* out,
-                          int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, int lpc, cudaStream_t s) {
+                          int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, int lpc, int ab_stride, int act, cudaStream_t s) {
   const int cpb = kScanThreads / lpc * CPT;
   const int vcols = vdim + ones_col;
   const size_t smem = ((size_t)2 * kScanChunk * lpc * EPL + (size_t)kScanChunk * cpb + kScanChunk) * sizeof(float);
@@ -134,7 +141,7 @@ static int launch_scan_as(const void* q, const void* k, const void* v, int q_str
   dim3 grid((vcols + cpb - 1) / cpb, H, R);
   launch_kernel(decay_scan_kernel<T, EPL, CPT>, dim3(grid), dim3(kScanThreads), smem, s, 1, (const T*)q, (const T*)k, (const T*)v,
                 q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, H, kq_heads, dim, vdim, ones_col,
-                q_scale, lpc);
+                q_scale, lpc, ab_stride, act);
   return launch_status();
 }
 
@@ -143,30 +150,33 @@ static int launch_scan_as(const void* q, const void* k, const void* v, int q_str
 template <typename T, int EPL>
 static int launch_scan(const void* q, const void* k, const void* v, int q_stride, int k_stride, int v_stride, const float* a,
                        const float* b, float* state, long slot_stride, const int* q_indptr, const int* state_slots, float* out,
-                       int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, cudaStream_t s) {
+                       int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, int ab_stride, int act, cudaStream_t s) {
   int lpc = 1;
   while (lpc * EPL < dim) lpc <<= 1;
   const int wide = kScanThreads / lpc * 4;
   const long blocks_wide = (long)((vdim + ones_col + wide - 1) / wide) * H * R;
   if (blocks_wide >= 148)
     return launch_scan_as<T, EPL, 4>(q, k, v, q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, R, H,
-                                     kq_heads, dim, vdim, ones_col, q_scale, lpc, s);
+                                     kq_heads, dim, vdim, ones_col, q_scale, lpc, ab_stride, act, s);
   return launch_scan_as<T, EPL, 1>(q, k, v, q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, R, H,
-                                   kq_heads, dim, vdim, ones_col, q_scale, lpc, s);
+                                   kq_heads, dim, vdim, ones_col, q_scale, lpc, ab_stride, act, s);
 }
 
-// q, k [T, kq_heads*dim] and v [T, H*vdim] in the activation type (row strides given); a, b float32 [T, H]; state: float32,
+// q, k [T, kq_heads*dim] and v [T, H*vdim] in the activation type (row strides given); a, b float32 [T, H] (ab_stride = H), or
+// one number a head for all tokens (ab_stride = 0: a float32 [H], b float32 [H] or null for ones: a memory with a constant
+// decay per head); act 1: silu on q, k and v as they are staged; state: float32,
 // a slot every slot_stride numbers, [H][vdim + ones_col][dim] at its start; out float32 [T, H, vdim + ones_col].
 ARLE_API int arle_decay_scan(const void* q, const void* k, const void* v, int dtype, int q_stride, int k_stride, int v_stride,
                              const float* a, const float* b, float* state, long slot_stride, const int* q_indptr,
                              const int* state_slots, float* out, int R, int H, int kq_heads, int dim, int vdim, int ones_col,
-                             float q_scale, cudaStream_t s) {
+                             float q_scale, int ab_stride, int act, cudaStream_t s) {
   if (R <= 0) return 0;
+  if (!a || (ab_stride != 0 && ab_stride != H) || (act != 0 && act != 1)) return ARLE_E_BADARG;
   if (H <= 0 || kq_heads <= 0 || H % kq_heads || dim <= 0 || vdim <= 0 || H > 65535 || R > 65535) return ARLE_E_BADARG;
   if (dim > 32 * 16) return ARLE_E_UNSUPPORTED;
 #define ARLE_SCAN(TT, E) \
   return launch_scan<TT, E>(q, k, v, q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, R, H, \
-                            kq_heads, dim, vdim, ones_col, q_scale, s)
+                            kq_heads, dim, vdim, ones_col, q_scale, ab_stride, act, s)
   if (dtype == 0) {
     if (dim <= 128) ARLE_SCAN(float, 4);
     if (dim <= 256) ARLE_SCAN(float, 8);

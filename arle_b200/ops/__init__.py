@@ -50,12 +50,16 @@ _SIGNATURES = {
     "arle_logit_cap": [_P, _F, ctypes.c_longlong, _P],
     "arle_gla_decay": [_P, _I, _I, _P, _P, _F, _P, _I, _I, _I, _P],
     "arle_gla_scan": [_P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
-    "arle_gla_out": [_P, _P, _I, _I, _P, _F, _F, _P, _I, _I, _I, _I, _P],
+    "arle_gla_out": [_P, _P, _I, _I, _P, _F, _F, _P, _I, _I, _I, _I, _I, _P],
     "arle_attention_prep": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_rotary_angles": [_P, _P, _P, _I, _I, _P],
-    "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _F, _I, _P],
-    "arle_attention_prep_post": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _F, _I, _F, _I, _P],
+    "arle_attention_prep_post": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "arle_branch_norm_add": [_P, _P, _I, _P, _P, _I, _I, _I, _F, _P],
+    "arle_branch_norm_add_norm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _F, _P],
+    "arle_rms_rows": [_P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
+    "arle_normed_sum": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _P],
+    "arle_bias_add": [_P, _I, _I, _P, _I, _I, _P],
     "arle_causal_conv": [_P, _I, _I, _P, _P, _P, _I, _P, ctypes.c_long, ctypes.c_long, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "arle_rglru_scan": [_P, _P, _P, _I, _I, _P, _P, _P, _P, _F, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_delta_gates": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
@@ -87,7 +91,7 @@ _SIGNATURES = {
     "arle_latent_prep": [_P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_latent_attention": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-    "arle_decay_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "arle_decay_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "arle_mlstm_gates": [_P, _I, _P, _P, _F, _P, _P, _P, ctypes.c_long, ctypes.c_long, _P, _P, _P, _I, _I, _P],
     "arle_mlstm_out": [_P, _P, _P, _I, _I, _P, _F, _P, _I, _I, _I, _I, _P],
     "arle_ssm_gates": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
@@ -521,8 +525,12 @@ def attention_prep(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_fr
 
 
 def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_table, nq: int, nkv: int, hd: int,
-                    page_size: int, scale: float, window, batch=None, vd: int = None, sink: float = None) -> None:
+                    page_size: int, scale: float, window, batch=None, vd: int = None, sink: float = None, keep_first: int = 0,
+                    softcap: float = None) -> None:
     """Causal attention of this step's queries over the paged cache.
+
+    ``keep_first``: with a window, the keys j < keep_first stay visible (at their true places) after the window has
+    passed them.  ``softcap``: a score s becomes softcap * tanh(s / softcap) before the softmax.
 
     ``vd``: the values' width when it differs from the keys' (the value cache is then [pages, nkv, page_size, vd] and
     out [T, nq*vd]).  ``sink``: the score of a sink without a value that the softmax's denominator counts besides the
@@ -549,7 +557,8 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
     _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _i32(block_table, "block_table")
     if block_table.stride(1) != 1:
         raise KernelError("paged_attention: block table rows must be contiguous")
-    if batch is not None and _KERNEL_SET == "fast" and vd == hd and fast_attention_supported(q, nq, nkv, hd):
+    keep_first = int(keep_first or 0) if window else 0
+    if batch is not None and _KERNEL_SET == "fast" and vd == hd and fast_attention_supported(q, nq, nkv, hd) and not keep_first and not softcap:
         if batch.max_q_len > 1:
             prefill = paged_attention_prefill_tc if tc_attention_supported(q, hd, page_size) else paged_attention_prefill
             prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
@@ -575,7 +584,8 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
     _check(library().arle_paged_attention_plain(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _dt(q), _ptr(positions), _ptr(row_of_token),
         _ptr(block_table), block_table.stride(0), nq, nkv, hd, vd, page_size, float(scale),
-        int(window) if window else 0, int(sink is not None), float(sink or 0.0), T, _stream()), "paged_attention")
+        int(window) if window else 0, int(sink is not None), float(sink or 0.0), keep_first, float(softcap or 0.0), T, _stream()),
+        "paged_attention")
 
 
 def _sink_arg(sink) -> float:
@@ -1020,8 +1030,9 @@ def gla_scan(q, k, v, alpha, state, q_indptr, state_slots, out, heads: int, dim:
            "gla_scan")
 
 
-def gla_out(o, gate, weight, eps: float, scale: float, out, heads: int, vdim: int) -> None:
-    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]) * scale.
+def gla_out(o, gate, weight, eps: float, scale: float, out, heads: int, vdim: int, gate_act: str = "silu") -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]) * scale (``gate_act`` "sigmoid": times
+    sigmoid(gate) instead).
     o float32 [T, heads*vdim] contiguous; gate (activation type, or None) and out may be slices of wider rows;
     weight float32 [vdim] or None."""
     T = o.shape[0]
@@ -1032,8 +1043,11 @@ def gla_out(o, gate, weight, eps: float, scale: float, out, heads: int, vdim: in
         raise KernelError("gla_out: gate and out must be [T, heads*vdim] of one type with unit inner stride")
     if weight is not None and (weight.dtype != torch.float32 or weight.numel() != vdim):
         raise KernelError("gla_out: weight must be float32 [vdim]")
+    if gate_act not in ("silu", "sigmoid"):
+        raise KernelError(f"gla_out: gate_act {gate_act!r} (silu, sigmoid)")
     _check(library().arle_gla_out(_ptr(o), _ptr(gate), _dt(out), gate.stride(0) if gate is not None else 0, _ptr(weight),
-                                  float(eps), float(scale), _ptr(out), out.stride(0), T, heads, vdim, _stream()), "gla_out")
+                                  float(eps), float(scale), _ptr(out), out.stride(0), T, heads, vdim, int(gate_act == "sigmoid"), _stream()),
+           "gla_out")
 
 
 # ------------------------------------------------------------------ a norm without statistics
@@ -1093,10 +1107,14 @@ def latent_prep(q, dkv, positions, slot_mapping, c_weight, eps: float, inv_freq,
     rank + dr], contiguous)."""
     T = q.shape[0]
     kd = rank + dr
-    if (q.stride(1) != 1 or dkv.stride(1) != 1 or q.shape[1] < heads * (dn + dr) or dkv.shape[1] < kd or q.dtype != dkv.dtype
-            or tuple(q_abs.shape) != (T, heads, kd) or not q_abs.is_contiguous() or q_abs.dtype != q.dtype):
+    if cache is None and dkv is None:               # nothing to store: only the queries' rotated numbers are prepared
+        dkv, c_weight = q, None
+    elif dkv is None or c_weight is None:
+        raise KernelError("latent_prep: a cache to store into needs dkv and the latent's norm weight")
+    if (q.stride(1) != 1 or dkv.stride(1) != 1 or q.shape[1] < heads * (dn + dr) or (cache is not None and dkv.shape[1] < kd)
+            or q.dtype != dkv.dtype or tuple(q_abs.shape) != (T, heads, kd) or not q_abs.is_contiguous() or q_abs.dtype != q.dtype):
         raise KernelError("latent_prep: q, dkv or q_abs do not fit the sizes given")
-    if c_weight.dtype != torch.float32 or c_weight.numel() != rank:
+    if c_weight is not None and (c_weight.dtype != torch.float32 or c_weight.numel() != rank):
         raise KernelError("latent_prep: the latent's norm weight must be float32 [rank]")
     if rot_dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
         raise KernelError("latent_prep: inv_freq must be float32 [rot_dims / 2]")
@@ -1157,22 +1175,29 @@ def latent_attention(q_abs, out, cache, positions, row_of_token, block_table, ra
 
 # ------------------------------------------------------------------ matrix memories with a scalar decay
 def decay_scan(q, k, v, a, b, state, q_indptr, state_slots, out, heads: int, kq_heads: int, dim: int, vdim: int,
-               ones_column: bool, q_scale: float) -> None:
+               ones_column: bool, q_scale: float, act: str = "none") -> None:
     """S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T (q_t * q_scale) over the tokens of every row of the step (row r owns
     tokens q_indptr[r] .. q_indptr[r+1]-1), from and into state[state_slots[r]].  q, k [T, kq_heads*dim] (head h reads
     head h // (heads / kq_heads)), v [T, heads*vdim], in the activation type (views of wider rows are fine); a, b float32
     [T, heads]; state float32 [slots, n] whose first heads * vcols * dim numbers are the memories, a head's transposed
     ([heads][vcols][dim]); vcols = vdim + 1 with ``ones_column`` (a column of ones beside v: it carries sum a..b k, the
-    normaliser of a matrix LSTM); out float32 [T, heads, vcols]."""
+    normaliser of a matrix LSTM); out float32 [T, heads, vcols].  A memory whose decay is one constant per head gives a as
+    float32 [heads] and b as float32 [heads] or None (ones).  ``act`` "silu": q, k and v go through silu as the kernel
+    reads them."""
     T = v.shape[0]
     R = state_slots.numel()
     vcols = vdim + int(bool(ones_column))
     if (q.shape != (T, kq_heads * dim) or k.shape != q.shape or v.shape != (T, heads * vdim) or q.dtype != k.dtype
             or q.dtype != v.dtype or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1):
         raise KernelError("decay_scan: q, k [T, kq_heads*dim] and v [T, heads*vdim] of one type with unit inner stride")
+    per_head = a.dim() == 1
+    if act not in ("none", "silu"):
+        raise KernelError(f"decay_scan: act {act!r} (none, silu)")
     for t_, n_ in ((a, "a"), (b, "b")):
-        if t_.dtype != torch.float32 or tuple(t_.shape) != (T, heads) or not t_.is_contiguous():
-            raise KernelError(f"decay_scan: {n_} must be contiguous float32 [T, heads]")
+        if t_ is None and per_head and n_ == "b":
+            continue
+        if t_ is None or t_.dtype != torch.float32 or tuple(t_.shape) != ((heads,) if per_head else (T, heads)) or not t_.is_contiguous():
+            raise KernelError(f"decay_scan: {n_} must be contiguous float32 [T, heads] (or [heads] for both)")
     if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < heads * vcols * dim or state.stride(1) != 1:
         raise KernelError(f"decay_scan: state {tuple(state.shape)} must be float32 [slots, >= {heads * vcols * dim}]")
     if out.dtype != torch.float32 or tuple(out.shape) != (T, heads, vcols) or not out.is_contiguous():
@@ -1182,7 +1207,8 @@ def decay_scan(q, k, v, a, b, state, q_indptr, state_slots, out, heads: int, kq_
         raise KernelError("decay_scan: q_indptr must have one entry more than state_slots")
     _check(library().arle_decay_scan(_ptr(q), _ptr(k), _ptr(v), _dt(q), q.stride(0), k.stride(0), v.stride(0), _ptr(a), _ptr(b),
                                      _ptr(state), state.stride(0), _ptr(q_indptr), _ptr(state_slots), _ptr(out), R, heads, kq_heads,
-                                     dim, vdim, vcols - vdim, float(q_scale), _stream()), "decay_scan")
+                                     dim, vdim, vcols - vdim, float(q_scale), 0 if per_head else heads, int(act == "silu"), _stream()),
+           "decay_scan")
 
 
 def mlstm_gates(pre, bias_i, bias_f, cap: float, q_indptr, state_slots, state, m_offset: int, a, b, floor) -> None:
@@ -1293,10 +1319,11 @@ def moe_select(z, correction, scratch, experts: int, top: int, groups: int, keep
     choice scores with ``correction`` (float32 [experts] or None) added, experts in ``groups`` equal groups of neighbours of
     which only the ``keep`` with the best scores (sum of a group's two largest choice scores) can be chosen; ids int32
     [T, top] in the order chosen, weights float32 [T, top] = sigmoid(z) * scale.  scratch float32 [T, experts + groups].
-    ``scores`` "softmax": the scores are softmax(z) over all experts; ``group_score`` "max": a group's score is its largest
-    choice score alone."""
+    ``scores`` "softmax": the scores are softmax(z) over all experts; "softmax_chosen": the sums z themselves decide the
+    choice and the weights are the softmax over the chosen sums alone; ``group_score`` "max": a group's score is its
+    largest choice score alone."""
     T = z.shape[0]
-    if scores not in ("sigmoid", "softmax") or group_score not in ("top2_sum", "max"):
+    if scores not in ("sigmoid", "softmax", "softmax_chosen") or group_score not in ("top2_sum", "max"):
         raise KernelError(f"moe_select: scores {scores!r} / group_score {group_score!r} not known")
     if z.dtype != torch.float32 or z.stride(1) != 1 or z.shape[1] < experts:
         raise KernelError("moe_select: z must be float32 [T, >= experts] with unit inner stride")
@@ -1308,7 +1335,8 @@ def moe_select(z, correction, scratch, experts: int, top: int, groups: int, keep
             or not ids.is_contiguous() or not weights.is_contiguous()):
         raise KernelError("moe_select: ids int32 [T, top] and weights float32 [T, top], contiguous")
     _check(library().arle_moe_select(_ptr(z), z.stride(0), _ptr(correction), _ptr(scratch), experts, top, groups, keep, float(scale),
-                                     int(scores == "softmax") | (int(group_score == "max") << 1), _ptr(ids), _ptr(weights), T,
+                                     int(scores == "softmax") | (int(group_score == "max") << 1) | (int(scores == "softmax_chosen") << 2),
+                                     _ptr(ids), _ptr(weights), T,
                                      _stream()), "moe_select")
 
 
@@ -1400,9 +1428,71 @@ def branch_norm_add(resid, branch, weight, eps: float, copy) -> None:
            "branch_norm_add")
 
 
+def branch_norm_add_norm(resid, branch, weight, eps: float, next_weight, next_eps: float, out) -> None:
+    """resid += branch / sqrt(mean(branch^2) + eps) * weight, then out = resid / sqrt(mean(resid^2) + next_eps) * next_weight,
+    per row, in float32, in one kernel: the norm on a sublayer's output and the norm on the next sublayer's input.  resid
+    float32 [T, H] contiguous; branch [T, H] (unit inner stride) and out [T, H] contiguous in the activation type; the
+    weights float32 [H]."""
+    T, H = resid.shape
+    if resid.dtype != torch.float32 or not resid.is_contiguous():
+        raise KernelError("branch_norm_add_norm: the residual must be contiguous float32")
+    if tuple(branch.shape) != (T, H) or branch.stride(1) != 1 or tuple(out.shape) != (T, H) or not out.is_contiguous() or out.dtype != branch.dtype:
+        raise KernelError("branch_norm_add_norm: branch [T, H] with unit inner stride, out contiguous [T, H] of the same type")
+    for w_ in (weight, next_weight):
+        if w_.dtype != torch.float32 or w_.numel() != H:
+            raise KernelError("branch_norm_add_norm: weights must be float32 [H]")
+    _check(library().arle_branch_norm_add_norm(_ptr(resid), _ptr(branch), branch.stride(0), _ptr(weight), _ptr(next_weight), _ptr(out),
+                                               _dt(out), T, H, float(eps), float(next_eps), _stream()), "branch_norm_add_norm")
+
+
+def rms_rows(x, weight, eps: float, out) -> None:
+    """out[t, :] = x[t, :] / sqrt(mean(x[t, :]^2) + eps) * weight (float32 [n] or None) for plain rows: x [T, n] float32 or in
+    out's type, out [T, n] in the activation type; both may be columns of wider rows."""
+    T, n = x.shape
+    if x.stride(1) != 1 or out.stride(1) != 1 or tuple(out.shape) != (T, n) or (x.dtype != out.dtype and x.dtype != torch.float32):
+        raise KernelError("rms_rows: x and out [T, n] with unit inner stride, x float32 or of out's type")
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != n):
+        raise KernelError("rms_rows: weight must be float32 [n]")
+    _check(library().arle_rms_rows(_ptr(x), _dt(x), x.stride(0), _ptr(weight), _ptr(out), _dt(out), out.stride(0), T, n, float(eps),
+                                   _stream()), "rms_rows")
+
+
+def normed_sum(xs, biases, weights, scales, eps: float, out) -> None:
+    """out = sum_m scales[m] * rmsnorm(xs[m] + biases[m]) * weights[m] per row, the norms over the whole row with ``eps``
+    inside the root: up to four members [T, H] in out's type (unit inner stride), biases float32 [H] or None each,
+    weights float32 [H]; float32 arithmetic, one rounding."""
+    n = len(xs)
+    T, H = out.shape
+    if not 0 < n <= 4 or len(weights) != n or len(scales) != n or (biases is not None and len(biases) != n):
+        raise KernelError("normed_sum: one to four members, a weight and a scale each")
+    biases = list(biases) if biases is not None else [None] * n
+    if out.stride(1) != 1:
+        raise KernelError("normed_sum: out must have unit inner stride")
+    for x_, b_, w_ in zip(xs, biases, weights):
+        if tuple(x_.shape) != (T, H) or x_.stride(1) != 1 or x_.dtype != out.dtype:
+            raise KernelError("normed_sum: members must be [T, H] of out's type with unit inner stride")
+        if w_.dtype != torch.float32 or w_.numel() != H or (b_ is not None and (b_.dtype != torch.float32 or b_.numel() != H)):
+            raise KernelError("normed_sum: weights (and biases) must be float32 [H]")
+    ptrs = (ctypes.c_void_p * n)(*[_ptr(x_) for x_ in xs])
+    bptrs = (ctypes.c_void_p * n)(*[_ptr(b_) for b_ in biases])
+    wptrs = (ctypes.c_void_p * n)(*[_ptr(w_) for w_ in weights])
+    strides = (ctypes.c_int * n)(*[x_.stride(0) for x_ in xs])
+    sc = (ctypes.c_float * n)(*[float(v) for v in scales])
+    _check(library().arle_normed_sum(ptrs, strides, bptrs, wptrs, sc, n, _ptr(out), _dt(out), out.stride(0), T, H, float(eps), _stream()),
+           "normed_sum")
+
+
+def bias_add(x, bias) -> None:
+    """x[t, :] += bias (float32 [n]) in place; x [T, n] with unit inner stride (columns of wider rows are fine)."""
+    T, n = x.shape
+    if x.stride(1) != 1 or bias.dtype != torch.float32 or bias.numel() != n:
+        raise KernelError("bias_add: x [T, n] with unit inner stride and bias float32 [n]")
+    _check(library().arle_bias_add(_ptr(x), _dt(x), x.stride(0), _ptr(bias), T, n, _stream()), "bias_add")
+
+
 def attention_prep_post(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim: int, k_cache, v_cache,
-                        nq: int, nkv: int, hd: int, vd: int, page_size: int) -> None:
-    """Rotation first, then the per-head norm x / sqrt(mean(x^2) + eps) (times a weight float32 [hd], or none), in place on
+                        nq: int, nkv: int, hd: int, vd: int, page_size: int, norm_first: bool = False) -> None:
+    """(``norm_first``: the norm and its weight come before the rotation instead of after it.)  Rotation first, then the per-head norm x / sqrt(mean(x^2) + eps) (times a weight float32 [hd], or none), in place on
     the q heads of qkv [T, nq*hd + nkv*hd + nkv*vd]; the k heads go the same way into k_cache [pages, nkv, page_size, hd]
     and the v heads as they are into v_cache [pages, nkv, page_size, vd] (nkv = 0: the rows hold q only and nothing is
     stored).  ``eps`` None: no norm.  Rotation as in ``attention_prep`` (number i with i + rotary_dim/2)."""
@@ -1427,8 +1517,8 @@ def attention_prep_post(qkv, positions, slot_mapping, q_weight, k_weight, eps, i
     _check(library().arle_attention_prep_post(
         _ptr(qkv), _dt(qkv), qkv.stride(0), _ptr(positions), _ptr(slot_mapping) if nkv else None, _ptr(q_weight), _ptr(k_weight),
         float(eps) if eps is not None else -1.0, _ptr(inv_freq) if rotary_dim else None, int(rotary_dim),
-        _ptr(k_cache) if nkv else None, _ptr(v_cache) if nkv else None, nq, nkv, hd, vd, page_size, T, _stream()),
-        "attention_prep_post")
+        _ptr(k_cache) if nkv else None, _ptr(v_cache) if nkv else None, nq, nkv, hd, vd, page_size, T, int(bool(norm_first)),
+        _stream()), "attention_prep_post")
 
 
 def causal_conv(x, in_bias, weight, out_bias, act: str, state, conv_offset: int, q_indptr, row_of_token, state_slots, out) -> None:

@@ -20,6 +20,14 @@ which elements turn together.  ``names`` gives the tensors' names after the pref
 stored weight); ``value_dim`` gives values another width than keys; ``sink`` adds a term exp(sink) without a value to the
 softmax's denominator; ``cache_window`` is what the cache keeps when other runs read this run's keys through wider windows
 than its own.
+
+The general form (any of ``keep_first``, ``softcap``, ``bias``, ``conv_taps``, or a per-head norm before the rotation with
+values of another width): ``keep_first`` keeps the first tokens of a sequence visible after the window has passed them (at
+their true positions); ``softcap`` turns a score s into softcap * tanh(s / softcap); ``bias`` adds stored biases in the q, k, v
+and output projections (tensor name + ``bias_suffix``); ``conv_taps`` runs a short causal convolution over time on every
+channel of q, k and v right after the projection (weights [channels, taps] under tensor name + ``conv_suffix``, zeros
+before a sequence's start; the last taps - 1 projected rows of a request are its state).  Its order is projection (+ bias)
+-> convolution -> per-head norm -> rotation -> cache -> attention -> output projection (+ bias).
 """
 from __future__ import annotations
 
@@ -29,7 +37,7 @@ from typing import ClassVar, Optional, Tuple
 import torch
 
 from .. import ops
-from .base import CacheNeed, Mixer, WeightDecl
+from .base import CacheNeed, Mixer, StateNeed, WeightDecl
 from .registry import build_part, register_part
 
 
@@ -53,6 +61,12 @@ class AttentionSpec:
     sink: Optional[float] = None    # score of a sink without a value in the softmax's denominator
     cache_window: Optional[int] = None   # what the cache keeps (None: ``window``); at least ``window``
     own_keys: bool = True           # False: no key and value projections; every run reads another run's cache
+    keep_first: int = 0             # with a window: the first tokens stay visible
+    softcap: Optional[float] = None  # scores <- softcap * tanh(scores / softcap)
+    bias: bool = False              # biases in the q, k, v and output projections
+    conv_taps: int = 0              # a short causal convolution on q, k and v (0: none)
+    bias_suffix: str = ".b"
+    conv_suffix: str = ".conv"
     kind: ClassVar[str] = "attention"
 
 
@@ -75,19 +89,27 @@ class Attention(Mixer):
             raise ValueError(f"attention: value_dim {self.vd} not supported (1 to 256)")
         if spec.cache_window is not None and (spec.window is None or spec.cache_window < spec.window):
             raise ValueError("attention: cache_window goes with a window and is at least as long")
+        if spec.keep_first < 0 or spec.conv_taps < 0 or (spec.softcap is not None and not spec.softcap > 0):
+            raise ValueError("attention: keep_first and conv_taps cannot be negative, softcap must be positive")
         self.spec = spec
         self.own_keys = spec.own_keys
+        self.general_form = bool(spec.keep_first or spec.softcap is not None or spec.bias or spec.conv_taps
+                                 or (spec.qk_norm == "head" and self.vd != spec.head_dim))
+        if self.general_form and (spec.qk_norm != "head" or spec.values != "projected" or spec.head_gate or spec.sink is not None
+                                  or not spec.own_keys or not spec.qk_norm_weight):
+            raise ValueError("attention: kept first tokens, capped scores, biases and the convolution go with a per-head norm before "
+                             "the rotation (or none), projected values, keys of its own, no gate and no sink")
         # rotation first and norm after it, values of another width, a sink: the later form, with kernels of its own
         self.post_form = spec.qk_norm == "head_after_rotation"
         if self.post_form and (spec.values != "projected" or spec.head_gate):
             raise ValueError("attention: a norm after the rotation goes with projected values and no gate")
-        if not self.post_form and (self.vd != spec.head_dim or spec.sink is not None or not spec.qk_norm_weight or not spec.own_keys):
+        if not self.post_form and not self.general_form and (self.vd != spec.head_dim or spec.sink is not None or not spec.qk_norm_weight or not spec.own_keys):
             raise ValueError("attention: value_dim, sink, a norm without weight and a run without keys of its own need qk_norm 'head_after_rotation'")
         self.position = build_part(spec.position) if spec.position is not None else None
         self.pairing = getattr(self.position, "pairing", "half")
         # the form the first kernels of this package were written for; everything else takes the general preparation
-        if self.post_form and self.pairing != "half":
-            raise ValueError("attention: a norm after the rotation goes with half-split rotation")
+        if (self.post_form or self.general_form) and self.pairing != "half":
+            raise ValueError("attention: a norm after the rotation, and the general form, go with half-split rotation")
         self.plain_form = (spec.qk_norm == "head" and spec.values == "projected" and not spec.head_gate
                            and self.pairing == "half")
         if not self.plain_form and spec.qk_norm == "head" and spec.qk_norm_eps is not None:
@@ -96,6 +118,8 @@ class Attention(Mixer):
         self.names.update(dict(spec.names or ()))
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
         self.gate_at = None             # column of the packed projection where the gate numbers start
+        self.b_qkv = self.b_o = self.w_conv = None
+        self.channels = spec.num_heads * spec.head_dim + spec.num_kv_heads * (spec.head_dim + self.vd)   # q | k | v
 
     # ---------------------------------------------------------------- weights
     def _name(self, role: str) -> str:
@@ -104,6 +128,18 @@ class Attention(Mixer):
     def weight_decls(self):
         s = self.spec
         dq, dkv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        if self.general_form:
+            rows = {"q": dq, "k": dkv, "v": s.num_kv_heads * self.vd}
+            decls = [WeightDecl(self._name(r), (n, s.hidden_size)) for r, n in rows.items()]
+            decls.append(WeightDecl(self._name("o"), (s.hidden_size, s.num_heads * self.vd)))
+            if s.bias:
+                decls += [WeightDecl(self._name(r) + s.bias_suffix, (n,), init="around_zero") for r, n in rows.items()]
+                decls.append(WeightDecl(self._name("o") + s.bias_suffix, (s.hidden_size,), init="around_zero"))
+            if s.conv_taps:
+                decls += [WeightDecl(self._name(r) + s.conv_suffix, (n, s.conv_taps), init="around_zero") for r, n in rows.items()]
+            if s.qk_norm_eps is not None:
+                decls += [WeightDecl(self._name("q_norm"), (s.head_dim,), init="gain"), WeightDecl(self._name("k_norm"), (s.head_dim,), init="gain")]
+            return tuple(decls)
         if self.post_form:
             decls = [WeightDecl(self._name("q"), (dq, s.hidden_size))]
             if self.own_keys:
@@ -147,6 +183,12 @@ class Attention(Mixer):
                 self.k_norm = tensors[self._name("k_norm")].to(device=device, dtype=torch.float32).contiguous()
         if self.position is not None:
             self.position.load(tensors, dtype, device)
+        if s.bias:
+            self.b_qkv = torch.cat([tensors[self._name(r) + s.bias_suffix].to(device=device, dtype=torch.float32) for r in ("q", "k", "v")]).contiguous()
+            self.b_o = tensors[self._name("o") + s.bias_suffix].to(device=device, dtype=torch.float32).contiguous()
+        if s.conv_taps:
+            self.w_conv = torch.cat([tensors[self._name(r) + s.conv_suffix].to(device=device, dtype=torch.float32) for r in ("q", "k", "v")],
+                                    dim=0).contiguous()
 
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
@@ -159,15 +201,23 @@ class Attention(Mixer):
     def cache_need(self):
         s = self.spec
         window = s.cache_window if s.cache_window is not None else s.window
+        keep = s.keep_first if window is not None else 0
         if self.vd != s.head_dim:
-            return CacheNeed(streams=((s.num_kv_heads, s.head_dim), (s.num_kv_heads, self.vd)), window=window)
-        return CacheNeed(s.num_kv_heads, s.head_dim, window)
+            return CacheNeed(streams=((s.num_kv_heads, s.head_dim), (s.num_kv_heads, self.vd)), window=window, keep_first=keep)
+        return CacheNeed(s.num_kv_heads, s.head_dim, window, keep_first=keep)
+
+    def state_need(self):
+        """The convolution's memory: a request's last taps - 1 projected rows of q | k | v, float32."""
+        if self.spec.conv_taps > 1:
+            n = self.channels * (self.spec.conv_taps - 1)
+            return StateNeed((-(-n // 4) * 4,), torch.float32)
+        return None
 
     def takes_scaled_rows(self, num_rows):
-        return not self.post_form and ops.fused_gemm_shape_ok(num_rows, self.w_qkv)
+        return not self.post_form and not self.general_form and ops.fused_gemm_shape_ok(num_rows, self.w_qkv)
 
     def can_sink(self, num_rows):
-        return not self.post_form and ops.fused_gemm_shape_ok(num_rows, self.w_o)
+        return not self.post_form and not self.general_form and ops.fused_gemm_shape_ok(num_rows, self.w_o)
 
     def _angles(self, qkv, ctx, inv_freq, rdim, general=False):
         """Cosines and sines of the step's positions, evaluated once for all layers that rotate by the same
@@ -205,9 +255,43 @@ class Attention(Mixer):
         ops.gemm(attn, self.w_o, out)
         return out
 
+    # ------------------------------------------------- biases, convolution, kept first tokens, capped scores
+    def _forward_general(self, x, ctx, cache, state):
+        s = self.spec
+        T = x.shape[0]
+        nq, nkv, hd, vd = s.num_heads, s.num_kv_heads, s.head_dim, self.vd
+        rot = self.position.rotary() if self.position is not None else None
+        inv_freq, rdim = rot if rot is not None else (None, 0)
+        if not cache.writable:
+            raise RuntimeError("attention: this form keeps keys of its own")
+        proj = ctx.ws.get("qkv", (T, self.channels), x.dtype)
+        ops.gemm(x, self.w_qkv, proj)
+        if s.conv_taps:
+            # the biases ride into the convolution as its input bias: added to a request's rows, not to the zeros before them
+            conv = ctx.ws.get("qkv_conv", (T, self.channels), x.dtype)
+            ops.causal_conv(proj, self.b_qkv, self.w_conv, None, "none", state if s.conv_taps > 1 else ctx.ws.get("conv_none", (1, 4), torch.float32),
+                            0, ctx.q_indptr, ctx.row_of_token, ctx.state_slots, conv)
+            proj = conv
+        elif s.bias:
+            ops.bias_add(proj, self.b_qkv)
+        if vd == hd:
+            ops.attention_prep(proj, ctx.positions, cache.slot_mapping, self.q_norm, self.k_norm, s.qk_norm_eps or 0.0, inv_freq, rdim,
+                               cache.k, cache.v, nq, nkv, hd, cache.page_size, angles=self._angles(proj, ctx, inv_freq, rdim))
+        else:
+            ops.attention_prep_post(proj, ctx.positions, cache.slot_mapping, self.q_norm, self.k_norm, s.qk_norm_eps, inv_freq, rdim,
+                                    cache.k, cache.v, nq, nkv, hd, vd, cache.page_size, norm_first=True)
+        attn = ctx.ws.get("attn_out", (T, nq * vd), x.dtype)
+        ops.paged_attention(proj[:, : nq * hd], attn, cache.k, cache.v, ctx.positions, ctx.row_of_token, cache.block_table,
+                            nq, nkv, hd, cache.page_size, s.scale, s.window, batch=ctx, vd=vd, keep_first=s.keep_first, softcap=s.softcap)
+        out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)
+        ops.gemm(attn, self.w_o, out)
+        if s.bias:
+            ops.bias_add(out, self.b_o)
+        return out
+
     # ------------------------------------------------- the general form, up to the output projection
     def pre_output_width(self):
-        return self.spec.num_heads * self.vd
+        return None if self.general_form else self.spec.num_heads * self.vd
 
     def output_weight(self):
         return self.w_o
@@ -248,6 +332,8 @@ class Attention(Mixer):
     def forward(self, x, ctx, cache, state, sink=None):
         s = self.spec
         T = x.shape[0]
+        if self.general_form:
+            return self._forward_general(x, ctx, cache, state)
         if self.post_form:
             return self._forward_post(x, ctx, cache)
         if not self.plain_form:

@@ -58,12 +58,15 @@ class CacheNeed:
     paged array ``[pages, heads, page_size, width]`` per layer, all under one block table.
 
     ``window`` None keeps every token; an integer keeps only what the last
-    ``window`` positions can still see, so older pages go back to the pool."""
+    ``window`` positions can still see, so older pages go back to the pool.
+    ``keep_first``: with a window, the first ``keep_first`` tokens of a request stay
+    visible for its whole life, so the pages that hold them are never given back."""
 
     num_kv_heads: int = 0
     head_dim: int = 0
     window: Optional[int] = None
     streams: Optional[Tuple[Tuple[int, int], ...]] = None
+    keep_first: int = 0
 
     def arrays(self) -> Tuple[Tuple[int, int], ...]:
         if self.streams is not None:
@@ -74,7 +77,7 @@ class CacheNeed:
         return sum(h * w for h, w in self.arrays())
 
     def group_key(self):
-        return (self.arrays(), self.window)
+        return (self.arrays(), self.window, self.keep_first if self.window is not None else 0)
 
 
 @dataclass(frozen=True)

@@ -131,3 +131,62 @@ class OutputNormBlock(Block):
 
 
 register_part(OutputNormBlockSpec.kind, OutputNormBlock)
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """x <- x + post(mixer(pre(x))); x <- x + post'(ffn(pre'(x))): a norm on every sublayer's input AND on its output (the
+    second half is absent when the spec names no feed-forward)."""
+    mixer_norm: object
+    mixer: object
+    mixer_post_norm: object
+    ffn_norm: object = None
+    ffn: object = None
+    ffn_post_norm: object = None
+    kind: ClassVar[str] = "sandwich_block"
+
+
+class SandwichBlock(Block):
+    """A sublayer's output norm, the sum into the 32-bit residual and the next sublayer's input norm are one kernel
+    (``ResidualStream.add_normed_before_norm``): the stream keeps the branch until the next ``normed(...)``."""
+
+    def __init__(self, spec: SandwichBlockSpec):
+        self.spec = spec
+        given = [spec.ffn is not None, spec.ffn_norm is not None, spec.ffn_post_norm is not None]
+        if any(given) != all(given):
+            raise ValueError("a block has a feed-forward with both of its norms, or none of the three")
+        self.mixer_norm = build_part(spec.mixer_norm)
+        self.mixer = build_part(spec.mixer)
+        self.mixer_post_norm = build_part(spec.mixer_post_norm)
+        self.ffn_norm = build_part(spec.ffn_norm) if spec.ffn is not None else None
+        self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
+        self.ffn_post_norm = build_part(spec.ffn_post_norm) if spec.ffn is not None else None
+        self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.ffn_norm, self.ffn, self.ffn_post_norm)
+                            if p is not None)
+        for n in (self.mixer_post_norm, self.ffn_post_norm):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ValueError(f"norm {type(n).__name__} cannot stand on a branch's output (no add_normed)")
+
+    def weight_decls(self):
+        return tuple(d for p in self._parts for d in p.weight_decls())
+
+    def load(self, tensors, dtype, device):
+        for p in self._parts:
+            p.load(tensors, dtype, device)
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self._parts)
+
+    def scratch_elements_per_token(self):
+        width = self.mixer_norm.scratch_elements_per_token()
+        return 2 * width + max(self.mixer.scratch_elements_per_token(), self.ffn.scratch_elements_per_token() if self.ffn is not None else 0)
+
+    def forward(self, stream, ctx, cache, state):
+        h = stream.normed(self.mixer_norm, "normed_a")
+        stream.add_normed_before_norm(self.mixer_post_norm, self.mixer.forward(h, ctx, cache, state))
+        if self.ffn is not None:
+            h = stream.normed(self.ffn_norm, "normed_b")
+            stream.add_normed_before_norm(self.ffn_post_norm, self.ffn.forward(h, ctx))
+
+
+register_part(SandwichBlockSpec.kind, SandwichBlock)

@@ -20,14 +20,19 @@ class GatedMlpSpec:
     prefix: str
     hidden_size: int
     intermediate_size: int
-    activation: str = "silu"        # "silu" or "gelu_tanh"
+    activation: str = "silu"        # "silu", "gelu_tanh" or "clamped_glu"
     names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")   # after the prefix
+    act_limit: float = 0.0          # "clamped_glu": g = min(gate x, limit), u = clamp(up x, +-limit), g sigmoid(act_alpha g) (u + 1)
+    act_alpha: float = 1.702
     kind: ClassVar[str] = "gated_mlp"
 
 
 class GatedMlp(FeedForward):
     def __init__(self, spec: GatedMlpSpec):
-        if spec.activation not in ops.ACTIVATIONS:
+        self.clamped = spec.activation == "clamped_glu"
+        if self.clamped and not spec.act_limit > 0:
+            raise ValueError("gated feed-forward: the clamped activation needs a positive act_limit")
+        if spec.activation not in ops.ACTIVATIONS and not self.clamped:
             raise ValueError(f"activation {spec.activation!r} not supported by the gated feed-forward "
                              f"({', '.join(ops.ACTIVATIONS)})")
         self.spec = spec
@@ -55,14 +60,14 @@ class GatedMlp(FeedForward):
         return 3 * self.spec.intermediate_size + self.spec.hidden_size
 
     def takes_scaled_rows(self, num_rows):
-        return ops.fused_gemm_shape_ok(num_rows, self.w_gate_up, gated=True)
+        return not self.clamped and ops.fused_gemm_shape_ok(num_rows, self.w_gate_up, gated=True)
 
     def can_sink(self, num_rows):
         return ops.fused_gemm_shape_ok(num_rows, self.w_down)
 
     # the feed-forward up to its last product
     def pre_output_width(self):
-        return self.spec.intermediate_size
+        return None if self.clamped else self.spec.intermediate_size
 
     def output_weight(self):
         return self.w_down
@@ -77,7 +82,11 @@ class GatedMlp(FeedForward):
         T = x.shape[0]
         gu = ctx.ws.get("gate_up", (T, 2 * s.intermediate_size), x.dtype)
         act = ctx.ws.get("ffn_act", (T, s.intermediate_size), x.dtype)
-        ops.gemm_act_mul(x, self.w_gate_up, gu, act, s.activation)
+        if self.clamped:
+            ops.gemm(x, self.w_gate_up, gu)
+            ops.clamped_glu(gu, act, s.act_limit, s.act_alpha)
+        else:
+            ops.gemm_act_mul(x, self.w_gate_up, gu, act, s.activation)
         out = ctx.ws.get("ffn_out", (T, s.hidden_size), x.dtype)
         if ops.gemm(act, self.w_down, out, sink=sink):
             return None                       # summed into the residual by the product itself

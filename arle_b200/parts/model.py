@@ -40,11 +40,31 @@ class ResidualStream:
         self._sink = None
         self._sinks_made = 0
         self._copy: Optional[torch.Tensor] = None       # the residual as it stands, in the activation type (or None)
+        self._normed_branch = None                      # (norm, branch): resid += norm(branch) still to be done
+
+    def _settle(self) -> None:
+        """Whatever ``add_normed_before_norm`` left to the next norm is summed into the residual now."""
+        if self._normed_branch is not None:
+            norm, branch = self._normed_branch
+            self._normed_branch = None
+            norm.add_normed(self.resid, branch, None)
+            self._copy = None
+
+    def add_normed_before_norm(self, norm, branch: torch.Tensor) -> None:
+        """resid += norm(branch) for a block whose next sublayer norms its input again: the sum waits for that
+        ``normed(...)``, which does both norms in one kernel when it can (``Norm.apply_after``)."""
+        self._settle()
+        if self.pending is not None:
+            ops.residual_add(self.resid, self.pending)
+            self.pending = None
+        self._normed_branch = (norm, branch)
+        self._copy = None
 
     def add(self, delta: Optional[torch.Tensor]) -> None:
         """``delta`` None: the branch has already put its output into the residual (through a sink)."""
         if delta is None:
             return
+        self._settle()
         if self.pending is not None:
             ops.residual_add(self.resid, self.pending)
         self.pending = delta
@@ -54,6 +74,7 @@ class ResidualStream:
     def plain(self, buffer_name: str) -> torch.Tensor:
         """The residual as a sublayer's input: itself in float32, its rounding to the activation type otherwise
         (written by the ``add_normed`` before it, or by a pass of its own at the model's first block)."""
+        self._settle()
         if self.pending is not None:
             ops.residual_add(self.resid, self.pending)
             self.pending = None
@@ -67,6 +88,7 @@ class ResidualStream:
 
     def add_normed(self, norm, branch: torch.Tensor, buffer_name: str) -> None:
         """resid += norm(branch), and the rounded residual for whoever reads it next, in one kernel."""
+        self._settle()
         if self.pending is not None:
             ops.residual_add(self.resid, self.pending)
             self.pending = None
@@ -78,6 +100,7 @@ class ResidualStream:
         """A sink for the branch that runs now, if the norm that follows it can be deferred and its
         reader takes rows without their factor; else None."""
         T = self.resid.shape[0]
+        self._settle()
         if (norm is None or reader is None or self.pending is not None or self.act_dtype != torch.bfloat16
                 or not self.resid.is_cuda or ops.kernel_set() != "fast" or not reader.takes_scaled_rows(T)):
             return None
@@ -101,6 +124,13 @@ class ResidualStream:
                     raise RuntimeError("a residual sink was filled for another norm than the one that runs next")
                 return ops.ScaledRows(sink.xs, sink.ss, sink.eps)
         out = self.ws.get(buffer_name, tuple(self.resid.shape), self.act_dtype)
+        if self._normed_branch is not None and self.pending is None and hasattr(norm, "apply_after"):
+            post, branch = self._normed_branch
+            if norm.apply_after(self.resid, branch, post, out):
+                self._normed_branch = None
+                self._copy = None
+                return out
+        self._settle()
         norm.apply(self.resid, self.pending, None, out, write_resid=self.pending is not None)
         if self.pending is not None:
             self._copy = None
@@ -109,6 +139,7 @@ class ResidualStream:
 
     def normed_rows(self, norm, rows: torch.Tensor, buffer_name: str) -> torch.Tensor:
         """Norm of the rows listed only (the residual itself is left as it is)."""
+        self._settle()
         out = self.ws.get(buffer_name, (rows.numel(), self.resid.shape[1]), self.act_dtype)
         norm.apply(self.resid, self.pending, rows, out, write_resid=False)
         return out

@@ -7,7 +7,8 @@ neighbours; a group's score is the sum of its two largest choice scores and only
 chosen.  An optional shared expert (a gated feed-forward of its own size) runs for every token and is added, times
 sigmoid(w_sg . x), one number per token, when it has such a gate.
 
-Variants, each a field of the spec: ``scores`` "softmax" takes the scores as a softmax over all experts; ``group_score``
+Variants, each a field of the spec: ``scores`` "softmax" takes the scores as a softmax over all experts; "softmax_chosen"
+chooses the experts with the largest router sums and weights them by the softmax over the chosen sums alone; ``group_score``
 "max" scores a group by its largest choice score alone; ``activation`` "clamped_glu" makes an expert
 down(g * sigmoid(act_alpha * g) * (u + 1)) with g = min(gate x, act_limit) and u = up x clamped to +-act_limit.
 
@@ -42,7 +43,7 @@ class RoutedExpertsSpec:
     shared_gate: bool = False        # the shared expert's output times sigmoid(w . x)
     activation: str = "silu"
     names: Optional[Tuple[Tuple[str, str], ...]] = None    # (role, name after the prefix); see DEFAULT_NAMES
-    scores: str = "sigmoid"          # or "softmax" (over all experts)
+    scores: str = "sigmoid"          # or "softmax" (over all experts), or "softmax_chosen" (the largest sums win, softmax over them alone)
     group_score: str = "top2_sum"    # or "max"
     act_limit: Optional[float] = None    # of the "clamped_glu" activation
     act_alpha: float = 1.702
@@ -64,7 +65,7 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"routed experts: activation {spec.activation!r}")
         if spec.activation == "clamped_glu" and not (spec.act_limit is not None and spec.act_limit > 0):
             raise ValueError("routed experts: the clamped activation needs a positive act_limit")
-        if spec.scores not in ("sigmoid", "softmax") or spec.group_score not in ("top2_sum", "max"):
+        if spec.scores not in ("sigmoid", "softmax", "softmax_chosen") or spec.group_score not in ("top2_sum", "max"):
             raise ValueError(f"routed experts: scores {spec.scores!r} / group_score {spec.group_score!r} not known")
         if spec.shared_gate and spec.shared is None:
             raise ValueError("routed experts: a shared gate needs a shared expert")

@@ -59,6 +59,14 @@ class RmsNorm(Norm):
         see ops.branch_norm_add."""
         ops.branch_norm_add(resid, branch, self.weight, self.eps, copy)
 
+    def apply_after(self, resid, branch, post, out) -> bool:
+        """resid += post(branch), then out = this norm of the new residual, in one kernel; False (nothing done) when
+        ``post`` is no RMS norm with a weight."""
+        if not isinstance(post, RmsNorm):
+            return False
+        ops.branch_norm_add_norm(resid, branch, post.weight, post.eps, self.weight, self.eps, out)
+        return True
+
 
 register_part(RmsNormSpec.kind, RmsNorm)
 

@@ -5,8 +5,13 @@ weights, y = sum_i scale_i * mixer_i(x).  When every member can stop before its 
 projection (``Mixer.pre_output_width``), each writes scale_i times that projection's input
 into its columns of one buffer and ONE product with the members' output matrices side by side
 gives y (the mixer then offers the same protocol itself); otherwise every member runs whole and
-the outputs are summed by a kernel.  At most one member may keep a paged cache and at most one a
-state per request (the model hands a schedule entry one of each).
+the outputs are summed by a kernel.  At most one member may keep a paged cache (the model hands a
+schedule entry one cache layer); members that keep a state per request share one row per request slot,
+each its own columns of it.
+
+``combine="normed"``: y = sum_i scale_i * rmsnorm(mixer_i(x)) * w_i, every member's output normed over the
+model width with a stored weight of its own (``norm_names``) before the sum: the members run whole and one
+kernel norms and adds them.
 
 ``ParallelBlock``: x <- x + (mixer(n) + ff(n)) with n = norm(x): one norm, both branches read its
 output; the feed-forward may be absent.  When mixer and feed-forward can both stop before their
@@ -23,7 +28,7 @@ from typing import ClassVar, Optional, Tuple
 import torch
 
 from .. import ops
-from .base import Block, Mixer
+from .base import Block, Mixer, StateNeed, WeightDecl
 from .registry import build_part, register_part
 
 
@@ -47,6 +52,9 @@ class ParallelMixerSpec:
     members: Tuple[object, ...]     # mixer specs
     scales: Tuple[float, ...]       # one per member
     hidden_size: int
+    combine: str = "sum"            # "sum": y = sum scale_i mixer_i(x); "normed": each output RMS-normed with its weight first
+    norm_names: Tuple[str, ...] = ()   # "normed": the members' norm weights, full tensor names
+    norm_eps: float = 0.0
     kind: ClassVar[str] = "parallel_mixer"
 
 
@@ -58,21 +66,40 @@ class ParallelMixer(Mixer):
         self.members = [build_part(m) for m in spec.members]
         self.with_cache = [i for i, m in enumerate(self.members) if m.cache_need() is not None]
         self.with_state = [i for i, m in enumerate(self.members) if m.state_need() is not None]
-        if len(self.with_cache) > 1 or len(self.with_state) > 1:
-            raise ValueError("a parallel mixer takes at most one member with a paged cache and one with a state")
+        if len(self.with_cache) > 1:
+            raise ValueError("a parallel mixer takes at most one member with a paged cache")
+        if spec.combine not in ("sum", "normed") or (spec.combine == "normed" and len(spec.norm_names) != len(spec.members)):
+            raise ValueError("a parallel mixer combines by 'sum' or 'normed', the latter with one norm weight's name per member")
+        if spec.combine == "normed" and len(spec.members) > 4:
+            raise ValueError("a parallel mixer norms and adds at most four members")
+        # members with a state: each gets its columns of one float32 row per request slot
+        self.state_at = {}
+        at = 0
+        for i in self.with_state:
+            need = self.members[i].state_need()
+            if len(self.with_state) > 1 and (need.dtype != torch.float32 or len(need.shape) != 1):
+                raise ValueError("members of a parallel mixer that share a state row need flat float32 states")
+            n = int(need.shape[0]) if len(need.shape) == 1 else 0
+            self.state_at[i] = (at, n)
+            at += -(-n // 4) * 4
+        self.state_width = at
+        self.norm_weights = None
         widths = [m.pre_output_width() for m in self.members]
-        self.shared_output = all(w is not None for w in widths)
+        self.shared_output = spec.combine == "sum" and all(w is not None for w in widths)
         self.widths = widths if self.shared_output else None
         self.w_o = None
         self.at = None
         self.padded = False
 
     def weight_decls(self):
-        return tuple(d for m in self.members for d in m.weight_decls())
+        own = tuple(WeightDecl(n, (self.spec.hidden_size,), init="gain") for n in self.spec.norm_names) if self.spec.combine == "normed" else ()
+        return tuple(d for m in self.members for d in m.weight_decls()) + own
 
     def load(self, tensors, dtype, device):
         for m in self.members:
             m.load(tensors, dtype, device)
+        if self.spec.combine == "normed":
+            self.norm_weights = [tensors[n].to(device=device, dtype=torch.float32).contiguous() for n in self.spec.norm_names]
         if self.shared_output:
             self.w_o, self.at = _side_by_side([m.output_weight() for m in self.members], self.widths)
             self.padded = any(-w % 8 for w in self.widths)
@@ -87,7 +114,11 @@ class ParallelMixer(Mixer):
         return self.members[self.with_cache[0]].cache_need() if self.with_cache else None
 
     def state_need(self):
-        return self.members[self.with_state[0]].state_need() if self.with_state else None
+        if not self.with_state:
+            return None
+        if len(self.with_state) == 1:
+            return self.members[self.with_state[0]].state_need()
+        return StateNeed((self.state_width,), torch.float32)
 
     def takes_scaled_rows(self, num_rows):
         return self.shared_output and all(m.takes_scaled_rows(num_rows) for m in self.members)
@@ -96,7 +127,11 @@ class ParallelMixer(Mixer):
         return self.shared_output and ops.fused_gemm_shape_ok(num_rows, self.w_o)
 
     def _args(self, i, cache, state):
-        return (cache if i in self.with_cache else None, state if i in self.with_state else None)
+        st = None
+        if i in self.with_state:
+            at, n = self.state_at[i]
+            st = state if len(self.with_state) == 1 else state[:, at: at + n]
+        return (cache if i in self.with_cache else None, st)
 
     # the mixer up to its one output product
     def pre_output_width(self):
@@ -121,6 +156,17 @@ class ParallelMixer(Mixer):
             self.forward_pre(x, ctx, cache, state, cat, 1.0)
             out = ctx.ws.get("mixer_out", (T, H), x.dtype)
             return None if ops.gemm(cat, self.w_o, out, sink=sink) else out
+        if self.spec.combine == "normed":
+            outs = []
+            for i, m in enumerate(self.members):
+                c, st = self._args(i, cache, state)
+                y = m.forward(x, ctx, c, st)
+                if any(y.data_ptr() == o.data_ptr() for o in outs):
+                    raise RuntimeError("parallel mixer: two members returned the same buffer; their outputs must live side by side")
+                outs.append(y)
+            out = ctx.ws.get("parallel_out", (T, H), x.dtype)
+            ops.normed_sum(outs, None, self.norm_weights, self.spec.scales, self.spec.norm_eps, out)
+            return out
         total = None
         for i, m in enumerate(self.members):
             c, st = self._args(i, cache, state)

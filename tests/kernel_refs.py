@@ -87,14 +87,14 @@ def attention_prep(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_fr
 
 
 def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_table, nq, nkv, hd, page_size, scale,
-                    window, batch=None, vd=None, sink=None):
+                    window, batch=None, vd=None, sink=None, keep_first=0, softcap=None):
     T = q.shape[0]
     g = nq // nkv
     vd = hd if vd is None else vd
     for t in range(T):
         p = int(positions[t])
         lo = max(0, p - window + 1) if window else 0
-        js = torch.arange(lo, p + 1)
+        js = torch.cat([torch.arange(0, min(int(keep_first or 0), lo)), torch.arange(lo, p + 1)])
         pages = block_table[int(row_of_token[t]), js // page_size].long()
         offs = js % page_size
         k = k_cache[pages, :, offs].to(F32)          # [n, nkv, hd]
@@ -102,6 +102,8 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
         qt = q[t].view(nq, hd).to(F32)
         for h in range(nq):
             s = (k[:, h // g] @ qt[h]) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
             if sink is None:
                 pr = torch.softmax(s, dim=0)
             else:                                            # one more term in the denominator, without a value
@@ -240,7 +242,7 @@ def gla_scan(q, k, v, alpha, state, q_indptr, state_slots, out, heads, dim, vdim
             out[t] = torch.einsum("hvd,hd->hv", S, qt).reshape(-1)
 
 
-def gla_out(o, gate, weight, eps, scale, out, heads, vdim):
+def gla_out(o, gate, weight, eps, scale, out, heads, vdim, gate_act="silu"):
     T = o.shape[0]
     y = o.view(T, heads, vdim)
     y = y * (1.0 / torch.sqrt((y * y).mean(dim=-1, keepdim=True) + eps))
@@ -249,7 +251,7 @@ def gla_out(o, gate, weight, eps, scale, out, heads, vdim):
     y = y.reshape(T, heads * vdim)
     if gate is not None:
         g = gate.to(F32)
-        y = y * (g / (1.0 + torch.exp(-g)))
+        y = y * ((g if gate_act == "silu" else 1.0) / (1.0 + torch.exp(-g)))
     out.copy_((y * scale).to(out.dtype))
 
 
@@ -290,8 +292,8 @@ def _turn_half(x, pos, inv_freq, dims):
 
 def latent_prep(q, dkv, positions, slot_mapping, c_weight, eps, inv_freq, rot_dims, cache, q_abs, heads, dn, dr, rank):
     T = q.shape[0]
-    kv = dkv[:, : rank + dr].to(F32)
     if cache is not None:
+        kv = dkv[:, : rank + dr].to(F32)
         c = kv[:, :rank]
         c = c * (1.0 / torch.sqrt((c * c).mean(dim=-1, keepdim=True) + eps)) * c_weight
         rec = torch.cat([c, _turn_half(kv[:, rank:], positions, inv_freq, rot_dims)], dim=-1).to(cache.dtype)
@@ -315,9 +317,15 @@ def latent_attention(q_abs, out, cache, positions, row_of_token, block_table, ra
 
 
 # ---------------------------------------------------------------- matrix memories with a scalar decay
-def decay_scan(q, k, v, a, b, state, q_indptr, state_slots, out, heads, kq_heads, dim, vdim, ones_column, q_scale):
+def decay_scan(q, k, v, a, b, state, q_indptr, state_slots, out, heads, kq_heads, dim, vdim, ones_column, q_scale, act="none"):
     vcols = vdim + int(bool(ones_column))
     rep = heads // kq_heads
+    T = v.shape[0]
+    if a.dim() == 1:                                # one decay (and one input weight) a head for all tokens
+        a = a[None, :].expand(T, heads)
+        b = torch.ones(T, heads) if b is None else b[None, :].expand(T, heads)
+    if act == "silu":
+        q, k, v = (x.to(F32) / (1.0 + torch.exp(-x.to(F32))) for x in (q, k, v))
     for r in range(state_slots.numel()):
         S = state[int(state_slots[r]), : heads * vcols * dim].view(heads, vcols, dim)
         for t in range(int(q_indptr[r]), int(q_indptr[r + 1])):
@@ -385,7 +393,10 @@ def gated_group_norm(y, x, skip, vdim, z, weight, eps, out, parts):
 
 # ---------------------------------------------------------------- routed experts
 def moe_select(z, correction, scratch, experts, top, groups, keep, scale, ids, weights, scores="sigmoid", group_score="top2_sum"):
-    s_ = torch.sigmoid(z[:, :experts]) if scores == "sigmoid" else torch.softmax(z[:, :experts], dim=-1)
+    if scores == "softmax_chosen":
+        s_ = z[:, :experts].clone()
+    else:
+        s_ = torch.sigmoid(z[:, :experts]) if scores == "sigmoid" else torch.softmax(z[:, :experts], dim=-1)
     ch = s_ + correction if correction is not None else s_.clone()
     per = experts // groups
     g = ch.view(-1, groups, per)
@@ -394,7 +405,7 @@ def moe_select(z, correction, scratch, experts, top, groups, keep, scale, ids, w
     ch = torch.where(kept[:, :, None].expand(-1, -1, per).reshape(-1, experts), ch, torch.full_like(ch, -math.inf))
     pick = ch.topk(top, dim=-1).indices
     ids.copy_(pick.to(torch.int32))
-    weights.copy_(s_.gather(1, pick) * scale)
+    weights.copy_((torch.softmax(s_.gather(1, pick), dim=-1) if scores == "softmax_chosen" else s_.gather(1, pick)) * scale)
 
 
 def moe_plan_size(experts, pairs):
@@ -446,13 +457,42 @@ def branch_norm_add(resid, branch, weight, eps, copy):
         copy.copy_(resid.to(copy.dtype))
 
 
+def branch_norm_add_norm(resid, branch, weight, eps, next_weight, next_eps, out):
+    b = branch.to(F32)
+    resid += b / torch.sqrt((b * b).mean(-1, keepdim=True) + eps) * weight
+    out.copy_((resid / torch.sqrt((resid * resid).mean(-1, keepdim=True) + next_eps) * next_weight).to(out.dtype))
+
+
+def rms_rows(x, weight, eps, out):
+    y = x.to(F32)
+    y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
+    out.copy_((y * weight if weight is not None else y).to(out.dtype))
+
+
+def normed_sum(xs, biases, weights, scales, eps, out):
+    total = 0.0
+    for i, x in enumerate(xs):
+        y = x.to(F32) + (biases[i] if biases is not None and biases[i] is not None else 0.0)
+        total = total + scales[i] * (y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)) * weights[i]
+    out.copy_(total.to(out.dtype))
+
+
+def bias_add(x, bias):
+    x.copy_((x.to(F32) + bias).to(x.dtype))
+
+
 def attention_prep_post(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, k_cache, v_cache,
-                        nq, nkv, hd, vd, page_size):
+                        nq, nkv, hd, vd, page_size, norm_first=False):
     T = qkv.shape[0]
     pos = positions.to(F32)
 
     def prepared(x, weight):                         # x [T, heads, hd]
         x = x.to(F32)
+        if norm_first:
+            if eps is not None:
+                x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+                x = x * weight if weight is not None else x
+            return _turn_half(x, pos, inv_freq, rotary_dim) if rotary_dim else x
         if rotary_dim:
             x = _turn_half(x, pos, inv_freq, rotary_dim)
         if eps is not None:
@@ -534,4 +574,5 @@ ALL = ("rotary_angles", "embedding", "rmsnorm", "residual_add", "gemm", "fused_g
        "act_mul", "gemm_act_mul", "attention_prep_row", "head_gate", "weighted_sum", "logit_cap", "gla_decay", "gla_scan", "gla_out",
        "dyt_norm", "gemm_heads", "latent_prep", "latent_attention", "decay_scan", "mlstm_gates", "mlstm_out", "ssm_gates", "conv_silu",
        "gated_group_norm", "moe_select", "moe_plan_size", "moe_plan", "moe_gemm", "moe_combine", "clamped_glu", "branch_norm_add",
-       "attention_prep_post", "causal_conv", "rglru_scan", "delta_gates", "delta_scan")
+       "attention_prep_post", "causal_conv", "rglru_scan", "delta_gates", "delta_scan", "branch_norm_add_norm", "rms_rows", "normed_sum",
+       "bias_add")
