@@ -269,7 +269,7 @@ class Attention(Mixer):
         if s.conv_taps:
             # the biases ride into the convolution as its input bias: added to a request's rows, not to the zeros before them
             conv = ctx.ws.get("qkv_conv", (T, self.channels), x.dtype)
-            ops.causal_conv(proj, self.b_qkv, self.w_conv, None, "none", state if s.conv_taps > 1 else ctx.ws.get("conv_none", (1, 4), torch.float32),
+            ops.causal_conv(proj, self.b_qkv, self.w_conv, None, "none", state if s.conv_taps > 1 else ctx.ws.get("conv_none", (ctx.cache.max_slots, 4), torch.float32),
                             0, ctx.q_indptr, ctx.row_of_token, ctx.state_slots, conv)
             proj = conv
         elif s.bias:

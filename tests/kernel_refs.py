@@ -487,7 +487,7 @@ def attention_prep_post(qkv, positions, slot_mapping, q_weight, k_weight, eps, i
     pos = positions.to(F32)
 
     def prepared(x, weight):                         # x [T, heads, hd]
-        x = x.to(F32)
+        x = x.to(F32).clone()
         if norm_first:
             if eps is not None:
                 x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
