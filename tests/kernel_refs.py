@@ -403,7 +403,7 @@ def moe_select(z, correction, scratch, experts, top, groups, keep, scale, ids, w
     gs = g.topk(min(2, per) if group_score == "top2_sum" else 1, dim=-1).values.sum(-1)
     kept = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, gs.topk(keep, dim=-1).indices, True)
     ch = torch.where(kept[:, :, None].expand(-1, -1, per).reshape(-1, experts), ch, torch.full_like(ch, -math.inf))
-    pick = ch.topk(top, dim=-1).indices
+    pick = torch.sort(ch, dim=-1, descending=True, stable=True).indices[:, :top]       # ties go to the lower index
     ids.copy_(pick.to(torch.int32))
     weights.copy_((torch.softmax(s_.gather(1, pick), dim=-1) if scores == "softmax_chosen" else s_.gather(1, pick)) * scale)
 
