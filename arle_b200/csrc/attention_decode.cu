@@ -20,6 +20,9 @@
 //   :239-463).
 // Rows whose step entry has more than one token are skipped (the prefill kernel
 // takes them).  The key range of a row is [max(0, kv_len - window), kv_len).
+// With keep_first > 0 the keys below keep_first that the window has passed are visible too: they stand in front of the
+// window's keys as whole tiles (the last one padded with masked places), so that no tile holds keys of both runs and the
+// splits cut the joined run.  With a cap, a score s (after the scale) becomes cap * tanh(s / cap) (tanhf).
 #include "common.cuh"
 #include "mma_utils.cuh"
 using namespace arle;
@@ -29,15 +32,17 @@ namespace {
 constexpr int kThreads = 128;
 constexpr int kTile = 64;   // keys per tile
 
-template <int HD>
+template <int HD, bool EXT>
 __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
     int bt_stride, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nq, int nkv,
-    int page_size, int ps_shift, float scale_log2, float sink_log2, int window, int splits) {
+    int page_size, int ps_shift, float scale_log2, float sink_log2, int window, int splits, int keep_first, float cap_arg,
+    float scale_over_cap) {
   pdl_launch_dependents();
   pdl_wait();
+  const float cap_log2 = EXT ? cap_arg : 0.f;
   constexpr int ROW = HD + 8;                 // padded row, in elements: 16 B more keeps ldmatrix conflict-free
   constexpr int CHUNKS = HD / 8;              // 16-byte chunks per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -52,10 +57,16 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
   if (q_indptr[r + 1] - t != 1) return;
   const int kv_len = kv_lens[r];
   const int lo = (window > 0 && kv_len > window) ? kv_len - window : 0;
-  const int span = kv_len - lo;
+  // places: [0, kap) the kept first keys (key = place, those from ka on masked), then the window's keys (key = lo + place - kap)
+  const int ka = EXT ? min(keep_first, lo) : 0;
+  const int kap = (ka + kTile - 1) / kTile * kTile;
+  const int span = kap + kv_len - lo;
   const int chunk = ((span + splits - 1) / splits + kTile - 1) / kTile * kTile;
-  const int beg = lo + split * chunk;
-  const int end = min(beg + chunk, kv_len);
+  const int beg = split * chunk;
+  const int end = min(beg + chunk, span);
+  // first key of the tile that starts at place v0, and the key after its last one
+  auto tile_first = [&](int v0) { return v0 < kap ? v0 : lo + v0 - kap; };
+  auto tile_end = [&](int v0) { return v0 < kap ? min(ka, min(end, v0 + kTile)) : lo + min(end, v0 + kTile) - kap; };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
 
@@ -76,16 +87,16 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
   // Page ids of a tile go to shared memory two tiles before its keys are fetched, so that
   // fetching a tile does not first wait for a block-table read.
   auto fetch_ids = [&](int tile, bool async) {
-    const int k0 = beg + tile * kTile;
-    if (k0 >= end) return;
-    const int first = k0 / page_size, last = (min(end, k0 + kTile) - 1) / page_size;
+    if (beg + tile * kTile >= end) return;
+    const int k0 = tile_first(beg + tile * kTile);
+    const int first = k0 / page_size, last = (tile_end(beg + tile * kTile) - 1) / page_size;
     if (tid <= last - first) {
       if (async) cp_async4(smem_u32(&pgbuf[tile & 3][tid]), bt + first + tid, 4);
       else pgbuf[tile & 3][tid] = bt[first + tid];
     }
   };
   auto load_tile = [&](int tile, int stage) {
-    const int k0 = beg + tile * kTile;
+    const int k0 = tile_first(beg + tile * kTile), kend = tile_end(beg + tile * kTile);
     const int first = ps_shift >= 0 ? (k0 >> ps_shift) : k0 / page_size;
     const int* pg = pgbuf[tile & 3];
     __nv_bfloat16* kd = ks + stage * kTile * ROW;
@@ -95,7 +106,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
       const int c = tid + i * kThreads;
       const int key = c / CHUNKS, part = c % CHUNKS;
       const int kj = k0 + key;
-      const bool ok = kj < end;
+      const bool ok = kj < kend;
       size_t off = 0;
       if (ok) {
         const int pidx = ps_shift >= 0 ? (kj >> ps_shift) : kj / page_size;     // pages are mostly a power of two
@@ -147,8 +158,9 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
       cp_wait<0>();
     }
     __syncthreads();
-    const int kbeg = beg + tile * kTile + warp * 16;       // this warp's 16 keys
-    if (kbeg < end) {
+    const int kbeg = tile_first(beg + tile * kTile) + warp * 16;       // this warp's 16 keys
+    const int kend = tile_end(beg + tile * kTile);
+    if (kbeg < kend) {
       const __nv_bfloat16* kt = ks + stage * kTile * ROW + warp * 16 * ROW;
       const __nv_bfloat16* vt = vs + stage * kTile * ROW + warp * 16 * ROW;
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -163,10 +175,17 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
         const int kj = kbeg + 8 * n + 2 * tq;
-        s[n][0] = kj < end ? s[n][0] * scale_log2 : -INFINITY;
-        s[n][1] = kj + 1 < end ? s[n][1] * scale_log2 : -INFINITY;
-        s[n][2] = kj < end ? s[n][2] * scale_log2 : -INFINITY;
-        s[n][3] = kj + 1 < end ? s[n][3] * scale_log2 : -INFINITY;
+        if (cap_log2 > 0.f) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[n][e] = cap_log2 * tanhf(s[n][e] * scale_over_cap);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[n][e] *= scale_log2;
+        }
+        s[n][0] = kj < kend ? s[n][0] : -INFINITY;
+        s[n][1] = kj + 1 < kend ? s[n][1] : -INFINITY;
+        s[n][2] = kj < kend ? s[n][2] : -INFINITY;
+        s[n][3] = kj + 1 < kend ? s[n][3] : -INFINITY;
         mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
         mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
       }
@@ -303,7 +322,7 @@ template <int HD>
 int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cache, const void* v_cache,
                   const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, float* part_o,
                   float* part_ml, int* counters, int nq, int nkv, int page_size, float scale, float sink, int window, int rows,
-                  int splits, cudaStream_t s) {
+                  int splits, int keep_first, float softcap, cudaStream_t s) {
   constexpr int ROW = HD + 8;
   int ps_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
@@ -311,17 +330,20 @@ int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cach
   const size_t tiles = (size_t)(4 * kTile + 16) * ROW * sizeof(__nv_bfloat16);
   const size_t merge = (size_t)(4 * 16 * HD + 128) * sizeof(float);
   const size_t smem = tiles > merge ? tiles : merge;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const bool ext = (window > 0 && keep_first > 0) || softcap > 0.f;
+  auto kernel = ext ? paged_decode_kernel<HD, true> : paged_decode_kernel<HD, false>;
+  static bool configured[2] = {false, false};
+  if (!configured[ext]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[ext] = true;
   }
   dim3 grid(rows, nkv, splits);
-  launch_kernel(paged_decode_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 1, 
+  launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, s, 1, 
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters, nq, nkv,
-      page_size, ps_shift, scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, splits);
+      page_size, ps_shift, scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, splits, window > 0 ? keep_first : 0,
+      softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, softcap > 0.f ? scale / softcap : 0.f);
   return launch_status();
 }
 
@@ -333,17 +355,18 @@ ARLE_API int arle_paged_attention_decode(const void* q, int q_row_stride, void* 
                                          const void* v_cache, const int* q_indptr, const int* kv_lens,
                                          const int* block_table, int bt_stride, float* part_o, float* part_ml,
                                          int* counters, int nq, int nkv, int hd, int page_size, float scale, float sink, int window,
-                                         int rows, int splits, cudaStream_t s) {
+                                         int rows, int splits, int keep_first, float softcap, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || page_size <= 0) return ARLE_E_UNSUPPORTED;
   if (splits < 1 || splits > 64 || nkv > 65535) return ARLE_E_UNSUPPORTED;
   if (splits > 1 && (!part_o || !part_ml || !counters)) return ARLE_E_BADARG;
   if ((q_row_stride % 8) != 0) return ARLE_E_UNSUPPORTED;     // 16-byte loads of q rows
+  if (keep_first < 0 || softcap < 0.f) return ARLE_E_BADARG;
   if (hd == 128)
     return launch_decode<128>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o,
-                              part_ml, counters, nq, nkv, page_size, scale, sink, window, rows, splits, s);
+                              part_ml, counters, nq, nkv, page_size, scale, sink, window, rows, splits, keep_first, softcap, s);
   if (hd == 64)
     return launch_decode<64>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o,
-                             part_ml, counters, nq, nkv, page_size, scale, sink, window, rows, splits, s);
+                             part_ml, counters, nq, nkv, page_size, scale, sink, window, rows, splits, keep_first, softcap, s);
   return ARLE_E_UNSUPPORTED;
 }

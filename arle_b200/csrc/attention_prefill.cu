@@ -14,6 +14,9 @@
 // A query i of a row with q_len queries and kv_len keys after the step stands at
 // position kv_len - q_len + i.  Rows with a single query are skipped when
 // skip_single is set (the decode kernel takes them).
+// With keep_first > 0 a windowed query also sees the keys below keep_first: the tiles that hold them (counted from key 0)
+// run before the window's tiles, under the same mask.  With a cap, a score s (after the scale) becomes cap * tanh(s / cap)
+// before the softmax (tanhf, not the approximate instruction: the cap multiplies its error).
 #include "common.cuh"
 #include "mma_utils.cuh"
 using namespace arle;
@@ -24,14 +27,18 @@ constexpr int kThreads = 128;
 constexpr int kBlockM = 64;
 constexpr int kTile = 64;
 
-template <int HD>
+// EXT: with kept first keys and a score cap (the usual form compiles without either).
+template <int HD, bool EXT>
 __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
-    int bt_stride, int nq, int nkv, int page_size, int ps_shift, float scale_log2, float sink_log2, int window, int skip_single) {
+    int bt_stride, int nq, int nkv, int page_size, int ps_shift, float scale_log2, float sink_log2, int window, int skip_single,
+    int keep_first_arg, float cap_arg, float scale_over_cap) {
   pdl_launch_dependents();
   pdl_wait();
+  const int keep_first = EXT ? keep_first_arg : 0;
+  const float cap_log2 = EXT ? cap_arg : 0.f;
   constexpr int ROW = HD + 8;
   constexpr int CHUNKS = HD / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -51,7 +58,12 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
   const int p_first = pos0 + mbeg, p_last = pos0 + mbeg + rows_here - 1;
   const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
   const int kb = lo / kTile * kTile;
-  const int ntiles = (p_last - kb) / kTile + 1;
+  const int nk = (min(keep_first, kb) + kTile - 1) / kTile;     // tiles of kept first keys that lie before the window's first tile
+  const int ntiles = nk + (p_last - kb) / kTile + 1;
+  auto tile_k0 = [&](int tile) { return tile < nk ? tile * kTile : kb + (tile - nk) * kTile; };
+  // the lowest and highest key of a tile that any query of the block may see
+  auto tile_lo = [&](int k0) { return k0 < keep_first ? k0 : max(lo, k0); };
+  auto tile_hi = [&](int tile, int k0) { return tile < nk ? min(k0 + kTile - 1, keep_first - 1) : min(p_last, k0 + kTile - 1); };
   const int kvh = h / (nq / nkv);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -63,8 +75,8 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
   const __nv_bfloat16* vbase = v_cache + (size_t)kvh * head_stride;
 
   auto fetch_ids = [&](int tile, bool async) {
-    const int k0 = max(lo, kb + tile * kTile);
-    const int k1 = min(p_last, kb + tile * kTile + kTile - 1);
+    const int k0 = tile_lo(tile_k0(tile));
+    const int k1 = tile_hi(tile, tile_k0(tile));
     if (k0 > k1) return;
     const int first = k0 / page_size, last = k1 / page_size;
     if (tid <= last - first) {
@@ -73,8 +85,9 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
     }
   };
   auto load_tile = [&](int tile, int stage) {
-    const int k0 = kb + tile * kTile;
-    const int first = ps_shift >= 0 ? (max(lo, k0) >> ps_shift) : max(lo, k0) / page_size;
+    const int k0 = tile_k0(tile);
+    const int tlo = tile_lo(k0), thi = tile_hi(tile, k0);
+    const int first = ps_shift >= 0 ? (tlo >> ps_shift) : tlo / page_size;
     const int* pg = pgbuf[tile & 3];
     __nv_bfloat16* kd = ks + stage * kTile * ROW;
     __nv_bfloat16* vd = vs + stage * kTile * ROW;
@@ -83,7 +96,7 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
       const int c = tid + i * kThreads;
       const int key = c / CHUNKS, part = c % CHUNKS;
       const int kj = k0 + key;
-      const bool ok = kj >= lo && kj <= p_last;
+      const bool ok = kj >= tlo && kj <= thi && (kj >= lo || kj < keep_first);
       size_t off = 0;
       if (ok) {
         const int pidx = ps_shift >= 0 ? (kj >> ps_shift) : kj / page_size;     // pages are mostly a power of two
@@ -144,8 +157,8 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
       cp_wait<0>();
     }
     __syncthreads();
-    const int k0 = kb + tile * kTile;
-    if (warp * 16 < rows_here && k0 <= warp_last && k0 + kTile > warp_first) {
+    const int k0 = tile_k0(tile);
+    if (warp * 16 < rows_here && k0 <= warp_last && (k0 + kTile > warp_first || k0 < keep_first)) {
       const __nv_bfloat16* kt = ks + stage * kTile * ROW;
       const __nv_bfloat16* vt = vs + stage * kTile * ROW;
       float s[8][4];
@@ -165,10 +178,17 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
         const int kj = k0 + 8 * n + 2 * tq;
-        s[n][0] = (kj <= prow0 && kj >= plo0) ? s[n][0] * scale_log2 : -INFINITY;
-        s[n][1] = (kj + 1 <= prow0 && kj + 1 >= plo0) ? s[n][1] * scale_log2 : -INFINITY;
-        s[n][2] = (kj <= prow1 && kj >= plo1) ? s[n][2] * scale_log2 : -INFINITY;
-        s[n][3] = (kj + 1 <= prow1 && kj + 1 >= plo1) ? s[n][3] * scale_log2 : -INFINITY;
+        if (cap_log2 > 0.f) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[n][e] = cap_log2 * tanhf(s[n][e] * scale_over_cap);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[n][e] *= scale_log2;
+        }
+        s[n][0] = (kj <= prow0 && (kj >= plo0 || kj < keep_first)) ? s[n][0] : -INFINITY;
+        s[n][1] = (kj + 1 <= prow0 && (kj + 1 >= plo0 || kj + 1 < keep_first)) ? s[n][1] : -INFINITY;
+        s[n][2] = (kj <= prow1 && (kj >= plo1 || kj < keep_first)) ? s[n][2] : -INFINITY;
+        s[n][3] = (kj + 1 <= prow1 && (kj + 1 >= plo1 || kj + 1 < keep_first)) ? s[n][3] : -INFINITY;
         mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
         mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
       }
@@ -239,23 +259,27 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
 template <int HD>
 int launch_prefill(const void* q, int q_row_stride, void* out, const void* k_cache, const void* v_cache,
                    const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, int nq, int nkv,
-                   int page_size, float scale, float sink, int window, int rows, int max_q_len, int skip_single, cudaStream_t s) {
+                   int page_size, float scale, float sink, int window, int rows, int max_q_len, int skip_single, int keep_first, float softcap,
+                   cudaStream_t s) {
   constexpr int ROW = HD + 8;
   int ps_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (ps_shift = 0; (1 << ps_shift) < page_size; ++ps_shift) {}
   const size_t smem = (size_t)(4 * kTile) * ROW * sizeof(__nv_bfloat16);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(paged_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const bool ext = (window > 0 && keep_first > 0) || softcap > 0.f;
+  auto kernel = ext ? paged_prefill_kernel<HD, true> : paged_prefill_kernel<HD, false>;
+  static bool configured[2] = {false, false};
+  if (!configured[ext]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[ext] = true;
   }
   dim3 grid((max_q_len + kBlockM - 1) / kBlockM, nq, rows);
-  launch_kernel(paged_prefill_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 1, 
+  launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, s, 1, 
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, nq, nkv, page_size, ps_shift,
-      scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, skip_single);
+      scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, skip_single, window > 0 ? keep_first : 0,
+      softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, softcap > 0.f ? scale / softcap : 0.f);
   return launch_status();
 }
 
@@ -265,15 +289,16 @@ ARLE_API int arle_paged_attention_prefill(const void* q, int q_row_stride, void*
                                           const void* v_cache, const int* q_indptr, const int* kv_lens,
                                           const int* block_table, int bt_stride, int nq, int nkv, int hd, int page_size,
                                           float scale, float sink, int window, int rows, int max_q_len, int skip_single,
-                                          cudaStream_t s) {
+                                          int keep_first, float softcap, cudaStream_t s) {
   if (rows <= 0 || max_q_len <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || nq > 65535 || rows > 65535) return ARLE_E_UNSUPPORTED;
   if ((q_row_stride % 8) != 0) return ARLE_E_UNSUPPORTED;
+  if (keep_first < 0 || softcap < 0.f) return ARLE_E_BADARG;
   if (hd == 128)
     return launch_prefill<128>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, nq,
-                               nkv, page_size, scale, sink, window, rows, max_q_len, skip_single, s);
+                               nkv, page_size, scale, sink, window, rows, max_q_len, skip_single, keep_first, softcap, s);
   if (hd == 64)
     return launch_prefill<64>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, nq,
-                              nkv, page_size, scale, sink, window, rows, max_q_len, skip_single, s);
+                              nkv, page_size, scale, sink, window, rows, max_q_len, skip_single, keep_first, softcap, s);
   return ARLE_E_UNSUPPORTED;
 }

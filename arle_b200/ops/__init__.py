@@ -65,14 +65,14 @@ _SIGNATURES = {
     "arle_delta_gates": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
     "arle_delta_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "arle_clamped_glu": [_P, _P, _I, _I, _I, _I, _F, _F, _P],
-    "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
+    "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _F, _P],
     "arle_paged_attention_decode_stream": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
                                            _F, _F, _I, _I, _I, _P, _P],
     "arle_paged_attention_decode_stream_prep": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
                                                 _F, _F, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P],
     "arle_decode_stream_plan_ints": [_I, _I],
     "arle_decode_stream_plan": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _P],
+    "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _I, _F, _P],
     "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I,
                                         _I, _I, _I, _P, _P],
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -558,12 +558,18 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
     if block_table.stride(1) != 1:
         raise KernelError("paged_attention: block table rows must be contiguous")
     keep_first = int(keep_first or 0) if window else 0
-    if batch is not None and _KERNEL_SET == "fast" and vd == hd and fast_attention_supported(q, nq, nkv, hd) and not keep_first and not softcap:
-        if batch.max_q_len > 1:
+    if batch is not None and _KERNEL_SET == "fast" and vd == hd and fast_attention_supported(q, nq, nkv, hd):
+        # kept first keys and capped scores are in the mma.sync prompt kernel and the split-KV decode kernel
+        extended = bool(keep_first or softcap)
+        if batch.max_q_len > 1 and extended:
+            paged_attention_prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
+                                    window, batch.max_q_len, skip_single=batch.num_single > 0, sink=sink, keep_first=keep_first,
+                                    softcap=softcap)
+        elif batch.max_q_len > 1:
             prefill = paged_attention_prefill_tc if tc_attention_supported(q, hd, page_size) else paged_attention_prefill
             prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
                     window, batch.max_q_len, skip_single=batch.num_single > 0, sink=sink)
-        if batch.num_single > 0 and stream_decode_supported(batch.num_rows, page_size, nq // nkv):
+        if batch.num_single > 0 and not extended and stream_decode_supported(batch.num_rows, page_size, nq // nkv):
             ctas = sm_count(q.device)
             slots = (ctas + batch.num_rows * nkv) * (nq // nkv)
             paged_attention_decode_stream(
@@ -572,14 +578,18 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
                 batch.ws.get("attn_piece_ml", (slots * 2,), torch.float32),
                 batch.ws.get_zeroed("attn_piece_counters", (batch.num_rows * nkv,), torch.int32), ctas, sink=sink)
         elif batch.num_single > 0:
-            splits = decode_splits(batch.num_rows, nkv, block_table.shape[1] * page_size, q.device)
+            bound = block_table.shape[1] * page_size
+            if window:
+                bound = min(bound, int(window) + keep_first + 63)
+            splits = decode_splits(batch.num_rows, nkv, bound, q.device)
             part_o = part_ml = counters = None
             if splits > 1:
                 part_o = batch.ws.get("attn_part_o", (batch.num_rows * nq * splits * hd,), torch.float32)
                 part_ml = batch.ws.get("attn_part_ml", (batch.num_rows * nq * splits * 2,), torch.float32)
                 counters = batch.ws.get_zeroed("attn_split_counters", (batch.num_rows * nkv,), torch.int32)
             paged_attention_decode(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd,
-                                   page_size, scale, window, splits, part_o, part_ml, counters, sink=sink)
+                                   page_size, scale, window, splits, part_o, part_ml, counters, sink=sink, keep_first=keep_first,
+                                   softcap=softcap)
         return
     _check(library().arle_paged_attention_plain(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _dt(q), _ptr(positions), _ptr(row_of_token),
@@ -736,7 +746,8 @@ def decode_splits(rows: int, nkv: int, kv_bound: int, device=None) -> int:
 
 
 def paged_attention_decode(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                           window, splits: int, part_o=None, part_ml=None, counters=None, sink: float = None) -> None:
+                           window, splits: int, part_o=None, part_ml=None, counters=None, sink: float = None, keep_first: int = 0,
+                           softcap: float = None) -> None:
     """Split-KV attention of the rows that have exactly one query (others are
     skipped).  q_indptr int32 [R+1], kv_lens int32 [R] (keys after this step).
     When splits > 1: part_o / part_ml are float32 scratch of R*nq*splits*hd and
@@ -751,11 +762,13 @@ def paged_attention_decode(q, out, k_cache, v_cache, q_indptr, kv_lens, block_ta
     _check(library().arle_paged_attention_decode(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_indptr), _ptr(kv_lens),
         _ptr(block_table), block_table.stride(0), _ptr(part_o), _ptr(part_ml), _ptr(counters), nq, nkv, hd, page_size,
-        float(scale), _sink_arg(sink), int(window) if window else 0, R, int(splits), _stream()), "paged_attention_decode")
+        float(scale), _sink_arg(sink), int(window) if window else 0, R, int(splits), int(keep_first or 0), float(softcap or 0.0),
+        _stream()), "paged_attention_decode")
 
 
 def paged_attention_prefill(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                            window, max_q_len: int, skip_single: bool = False, sink: float = None) -> None:
+                            window, max_q_len: int, skip_single: bool = False, sink: float = None, keep_first: int = 0,
+                            softcap: float = None) -> None:
     """Flash-attention over the paged cache for rows with several queries (and,
     unless skip_single, for single-query rows too)."""
     R = kv_lens.numel()
@@ -763,7 +776,8 @@ def paged_attention_prefill(q, out, k_cache, v_cache, q_indptr, kv_lens, block_t
     _check(library().arle_paged_attention_prefill(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_indptr), _ptr(kv_lens),
         _ptr(block_table), block_table.stride(0), nq, nkv, hd, page_size, float(scale),
-        _sink_arg(sink), int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _stream()), "paged_attention_prefill")
+        _sink_arg(sink), int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), int(keep_first or 0),
+        float(softcap or 0.0), _stream()), "paged_attention_prefill")
 
 
 # ------------------------------------------------------------------ activation

@@ -214,6 +214,59 @@ def test_routing_by_a_softmax_over_the_chosen():
         torch.testing.assert_close(res[1][0].sum(-1), torch.ones(T), rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("cap", [None, 3.0])
+@pytest.mark.parametrize("nq,nkv,hd,ps,window,keep", [(8, 2, 128, 16, 37, 20), (4, 1, 64, 16, 33, 5), (2, 2, 64, 32, 300, 100), (12, 4, 128, 8, 64, 64),
+                                                       (4, 4, 64, 16, 40, 0), (4, 2, 128, 16, None, 7)])
+def test_kept_first_keys_and_capped_scores_in_the_tensor_core_attention_kernels(nq, nkv, hd, ps, window, keep, cap):
+    """Prompts on mma.sync and decoding with split keys (one split and several), with requests shorter than what is kept,
+    shorter than the window, and far longer than both: each against the plain statement, which differs from the attention
+    without the kept keys, and from the one without the cap, by far more than the tolerance.  The pages that no query can
+    see hold poison."""
+    import math
+
+    from test_kernels_gpu import _fast_setup
+
+    scale = 4.0 / math.sqrt(hd)
+
+    def want(q, kc, vc, pos, rows, bt, keep_, cap_):
+        exp = torch.empty(q.shape[0], nq * hd, dtype=torch.bfloat16)
+        kernel_refs.paged_attention(q.cpu(), exp, kc.cpu(), vc.cpu(), pos.cpu(), rows.cpu(), bt.cpu(), nq, nkv, hd, ps, scale, window,
+                                    keep_first=keep_, softcap=cap_)
+        return exp.float()
+
+    def poison(kc, vc, bt, lens, q_lens):
+        if not window:
+            return
+        for r, (n, ql) in enumerate(zip(lens, q_lens)):
+            for p in range(-(-keep // ps), max(0, n - ql - window + 1) // ps):
+                kc[bt[r, p]] = 1e3
+                vc[bt[r, p]] = float("nan")
+
+    lens, q_lens = [130, 300, 128, 129, 9, 700], [130, 2, 128, 3, 1, 333]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=6)
+    poison(kc, vc, bt, lens, q_lens)
+    exp = want(q, kc, vc, pos, rows, bt, keep, cap)
+    if window and keep:
+        assert (exp - want(q, kc, vc, pos, rows, bt, 0, cap)).abs().max() > 0.05
+    if cap:
+        assert (exp - want(q, kc, vc, pos, rows, bt, keep, None)).abs().max() > 0.05
+    out = torch.zeros(q.shape[0], nq * hd, dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_prefill(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, scale, window, max(q_lens), keep_first=keep, softcap=cap)
+    ops.check_errors(DEV)
+    torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+    lens = [1, 63, 64, 65, 700, 2049, 17, keep + 1, (window or 50) + keep]
+    R = len(lens)
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, [1] * R, seed=3)
+    poison(kc, vc, bt, lens, [1] * R)
+    exp = want(q, kc, vc, pos, rows, bt, keep, cap)
+    for splits in (1, 2, 5):
+        out = torch.zeros(R, nq * hd, dtype=torch.bfloat16, device=DEV)
+        po, pml = torch.zeros(R * nq * splits * hd, device=DEV), torch.zeros(R * nq * splits * 2, device=DEV)
+        ops.paged_attention_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, scale, window, splits, po, pml,
+                                   torch.zeros(R * nkv, dtype=torch.int32, device=DEV), keep_first=keep, softcap=cap)
+        torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+
+
 # ------------------------------------------------------------------ the engine under every cutting
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
