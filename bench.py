@@ -19,6 +19,9 @@ single-GPU one: for --gpus above 1 it says so and exits with 2.
 beside as many Qwen3 layers of equal sizes, prefill and decode, with every kernel's time per layer.
 ``--design zuderax`` does the same for Zuderax layers (a latent attention, a matrix LSTM and a Mamba-2 layer in turn,
 every second feed-forward one of routed experts) beside Kolodra and Qwen3 layers of equal width.
+``--design lukinex`` does the same for Lukinex layers (an attention whose window keeps the first tokens, two latent attentions
+of which the second reads the first one's latents, and a parallel mixer of a capped attention with biases and a short
+convolution beside a memory with constant decays, all with routed feed-forwards) beside Lasupel and Zuderax layers.
 ``--design lasupel`` does the same for Lasupel layers (an attention with a sliding window and a sink, an RG-LRU layer, an
 attention that reads the first one's keys and values, a gated delta rule layer, in turn; the first feed-forward of four
 dense, the others routed experts) beside Zuderax and Qwen3 layers of equal width.
@@ -209,6 +212,39 @@ def lasupel_config(z, ll, L, window):
     return {"architecture": "Lasupel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": layers}
 
 
+# Mixer sizes for ``--design lukinex`` at the same widths: the attention's heads are the Qwen3 layer's (a window of half the
+# benchmark's context that keeps the first 64 tokens, a quarter of a head rotated with divided frequencies), the latent
+# attention keeps a latent of 256 / 512 numbers (every second one reads the one before it), the parallel mixer has half the
+# attention heads on its softmax side (biases, four taps, scores capped at 30) beside memories of 128 x 128 with constant
+# decays, and the chosen experts together with the shared one are as wide as the dense feed-forward.
+LUKINEX_SIZES = {"0.6b": dict(latent=(16, 64, 64, 256, 512), right=8, experts=16, top=3),
+                 "8b": dict(latent=(32, 128, 128, 512, 1536), right=16, experts=32, top=3)}
+
+
+def lukinex_config(z, kk, L, window):
+    routed = {"kind": "moe", "expert": {"ff": z["ff"] // (kk["top"] + 1), "limit": 7.0}, "shared": {"ff": z["ff"] // (kk["top"] + 1), "limit": 7.0},
+              "router": {"experts": kk["experts"], "top": kk["top"]}}
+    mask = {"size": window, "keep_first": 64}
+    attn = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5, "mask": mask,
+            "rot": {"base": 1e6, "dims": z["hd"] // 4, "scaling": {"factor": 2.0}}}
+    h, dk, dv, rank, qrank = kk["latent"]
+    lat = {"heads": h, "dim": dk, "vdim": dv, "kv_rank": rank, "q_rank": qrank, "scale": dk ** -0.5}
+    left = {"heads": z["heads"] // 2, "kv_heads": max(1, z["kv"] // 2), "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5, "mask": mask,
+            "rot": {"base": 1e6, "dims": z["hd"]}, "conv": 4, "softcap": 30.0}
+    right = {"heads": kk["right"], "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 7 * i / max(1, kk["right"] - 1)) for i in range(kk["right"])]}
+    layers = []
+    for i in range(L):
+        if i % 4 == 0:
+            layers.append({"type": "attention", "mixer": dict(attn), "mlp": routed})
+        elif i % 4 == 1:
+            layers.append({"type": "latent_attention", "mixer": dict(lat), "mlp": routed})
+        elif i % 4 == 2:
+            layers.append({"type": "latent_attention", "mixer": dict(lat, kv_from=i - 1), "mlp": routed})
+        else:
+            layers.append({"type": "parallel", "mixer": {"left": dict(left), "right": dict(right)}, "mlp": routed})
+    return {"architecture": "Lukinex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "layers": layers}
+
+
 def design_table(args, torch, ops, pk) -> int:
     """``--design kolodra``: prefill and decode throughput of a few Kolodra layers beside the same number of Qwen3
     layers of equal width, heads and feed-forward, with the device time of every kernel of one step (profiler
@@ -218,7 +254,7 @@ def design_table(args, torch, ops, pk) -> int:
     from arle_b200.engine import ModelRunner, StepEntry, random_model
 
     dev = torch.device("cuda:0")
-    L, T, C = args.layers or (6 if args.design == "zuderax" else (8 if args.design == "lasupel" else 4)), args.prefill_tokens, args.context
+    L, T, C = args.layers or (6 if args.design == "zuderax" else (8 if args.design in ("lasupel", "lukinex") else 4)), args.prefill_tokens, args.context
     gen = torch.Generator().manual_seed(1)
     out = {"design": args.design, "layers": L, "prefill_tokens": T, "context": C, "dtype": "bf16", "peaks": pk, "sizes": {}}
 
@@ -326,6 +362,12 @@ def design_table(args, torch, ops, pk) -> int:
             if not args.design_alone:
                 out["sizes"][name].update({"zuderax": measure(zuderax_config(z, ZUDERAX_SIZES[name], L, max(C // 2, 16))),
                                            "qwen3": measure(qwen_config(z))})
+        elif args.design == "lukinex":
+            out["sizes"][name]["mixers"] = LUKINEX_SIZES[name]
+            out["sizes"][name]["lukinex"] = measure(lukinex_config(z, LUKINEX_SIZES[name], L, max(C // 2, 16)))
+            if not args.design_alone:
+                out["sizes"][name].update({"lasupel": measure(lasupel_config(z, LASUPEL_SIZES[name], L, max(C // 2, 16))),
+                                           "zuderax": measure(zuderax_config(z, ZUDERAX_SIZES[name], L, max(C // 2, 16)))})
         elif not args.design_alone:
             out["sizes"][name].update({"kolodra": measure(kolodra_config(z)), "qwen3": measure(qwen_config(z))})
     print(json.dumps(out))
@@ -354,8 +396,8 @@ def main() -> int:
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--no-kernel-times", action="store_true",
                     help="with --design: leave out the per-kernel times (they come from torch's profiler, which cannot run under another profiler)")
-    ap.add_argument("--design-alone", action="store_true", help="with --design zuderax or lasupel: leave out the models it stands beside")
-    ap.add_argument("--design", default=None, choices=["kolodra", "zuderax", "lasupel"],
+    ap.add_argument("--design-alone", action="store_true", help="with --design zuderax, lasupel or lukinex: leave out the models it stands beside")
+    ap.add_argument("--design", default=None, choices=["kolodra", "zuderax", "lasupel", "lukinex"],
                     help="instead of the default workload: a few layers of this design beside as many Qwen3 layers of equal "
                          "sizes, prefill and decode, with every kernel's time (uses --layers, --steps, --context, --prefill-tokens)")
     ap.add_argument("--timeline", action="store_true",
