@@ -69,8 +69,8 @@ def _attention_keys(m: dict, w: str, prefix: str = "", left: bool = False) -> di
     out = {k: _under(w, _pos_int, m, k) for k in ("heads", "kv_heads", "dim", "vdim")}
     if out["heads"] % out["kv_heads"]:
         fail(f"'heads' ({out['heads']}) must be a multiple of 'kv_heads' ({out['kv_heads']})")
-    if out["dim"] % 2 or out["dim"] > 256 or out["vdim"] > 256:
-        fail(f"'dim' = {out['dim']} must be even and, like 'vdim' = {out['vdim']}, at most 256")
+    if out["dim"] > 256 or out["vdim"] > 256:
+        fail(f"'dim' = {out['dim']} and 'vdim' = {out['vdim']} may be at most 256")
     out["scale"] = float(_under(w, _get, m, "scale"))
     mask = m.get("mask")
     out["window"] = _under(w, _pos_int, m, "mask.size") if mask is not None else None
@@ -86,15 +86,15 @@ def _attention_keys(m: dict, w: str, prefix: str = "", left: bool = False) -> di
         fail(f"'rot.dims' = {out['rot_dims']} must be even and at most dim ({out['dim']})")
     if out["rot_dims"] and not (out["rot_base"] > 0 and out["rot_divide"] > 0):
         fail("'rot.base' and 'rot.scaling.factor' must be positive")
+    cap = m.get("softcap")
+    if cap is not None and (isinstance(cap, bool) or not isinstance(cap, (int, float)) or not float(cap) > 0):
+        fail(f"'softcap' = {cap!r} must be positive")
+    out["softcap"] = float(cap) if cap is not None else None
     if left:
         conv = m.get("conv", 0)
         if isinstance(conv, bool) or not isinstance(conv, int) or conv < 0:
             fail(f"'conv' = {conv!r} must be a number of taps")
         out["conv"] = conv
-        cap = m.get("softcap")
-        if cap is not None and not float(cap) > 0:
-            fail(f"'softcap' = {cap!r} must be positive")
-        out["softcap"] = float(cap) if cap is not None else None
     return {prefix + k: v for k, v in out.items()}
 
 
@@ -124,8 +124,8 @@ def _mixer(kind: str, m: dict, w: str) -> Tuple[Tuple[str, object], ...]:
         out.update({"right." + k: _under(wr, _pos_int, r, k) for k in ("heads", "dim", "vdim")})
         decay = r.get("decay")
         if (not isinstance(decay, list) or len(decay) != out["right.heads"]
-                or not all(isinstance(d, (int, float)) and not isinstance(d, bool) and 0.0 < d <= 1.0 for d in decay)):
-            raise ConfigError(f"config.json: {wr}.decay must list one number in (0, 1] for each of the {out['right.heads']} heads")
+                or not all(isinstance(d, (int, float)) and not isinstance(d, bool) and 0.0 <= d < float("inf") for d in decay)):
+            raise ConfigError(f"config.json: {wr}.decay must list one number (not negative) for each of the {out['right.heads']} heads")
         out["right.decay"] = tuple(float(d) for d in decay)
     return tuple(sorted(out.items(), key=lambda kv: kv[0]))
 
@@ -210,7 +210,7 @@ class LukinexConfig:
             qk_norm_eps=None if left else self.norm_eps,
             position=RotarySpec(rotary_dim=m("rot_dims"), theta=m("rot_base"), pairing="half", divide_by=m("rot_divide")) if m("rot_dims") else None,
             window=m("window"), qk_norm="head", names=(("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"), ("q_norm", "q.norm"), ("k_norm", "k.norm")),
-            value_dim=m("vdim"), keep_first=m("keep_first") if m("window") is not None else 0, softcap=m("softcap") if left else None,
+            value_dim=m("vdim"), keep_first=m("keep_first") if m("window") is not None else 0, softcap=m("softcap"),
             bias=left, conv_taps=m("conv") if left else 0)
 
     def _mixer_spec(self, l: LukinexLayer, p: str):

@@ -12,7 +12,8 @@
 //  * decay_scan: a block per (row of the step, head, tile of columns).  A column of S (dim numbers, stored
 //    contiguously: the state is kept transposed, [head][column][dim]) is held by `lpc` lanes, EPL numbers a lane;
 //    the lanes add their parts of o_t by shuffles; a thread holds one column, or four that share its loads of k and q.
-//    q, k, b v and a of 16 tokens are staged in shared memory, then the 16 steps run from there.  The split of a column depends on dim alone, so a token's sums have one order
+//    q, k, b v and a of 16 tokens are staged in shared memory, then the 16 steps run from there, while the next 16 tokens'
+//    numbers are already on their way into registers.  The split of a column depends on dim alone, so a token's sums have one order
 //    whatever the cutting or the batch.
 //  * mlstm_gates: the log gates of the matrix LSTM (soft-capped), its running maximum m (carried in the state),
 //    and from them a_t, b_t and exp(-m_t); the gates of 128 tokens are evaluated side by side, the maximum runs
@@ -58,30 +59,94 @@ __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
 #pragma unroll
     for (int i = 0; i < EPL; ++i) S[j][i] = (c0 + cl0 + j < vcols && e0 + i < dim) ? sp[(size_t)(c0 + cl0 + j) * dim + e0 + i] : 0.f;
 
+  // Rows of more than one chunk: the NEXT chunk's q, k, v, a and b are asked for before this chunk's steps run and wait in
+  // registers (as they lie in memory) until the steps are done; the chain of steps then never waits for memory.  A thread
+  // holds at most NQ numbers of q and of k (16 tokens x 32 lanes x EPL / 256 threads) and NV of v.
+  constexpr int NQ = 2 * EPL;
+  constexpr int NV = 2;
+  constexpr bool PRE = EPL <= 8;
+  const bool vpre = PRE && kScanChunk * cpb <= NV * kScanThreads;
+  const int dshift = __ffs(dpad) - 1;                    // dpad is a power of two
+  T rq[PRE ? NQ : 1], rk[PRE ? NQ : 1], rv[NV];
+  float rb[NV], ra = 0.f;
+  auto ask = [&](int t0, int n) {
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+      const int idx = threadIdx.x + i * kScanThreads;
+      const int tt = idx >> dshift, e = idx & (dpad - 1);
+      const bool in = idx < n * dpad && e < dim;
+      rq[i] = in ? q[(size_t)(t0 + tt) * q_stride + (size_t)g * dim + e] : from_f32<T>(0.f);
+      rk[i] = in ? k[(size_t)(t0 + tt) * k_stride + (size_t)g * dim + e] : from_f32<T>(0.f);
+    }
+    if (vpre) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int idx = threadIdx.x + i * kScanThreads;
+        const int tt = idx / cpb, c = c0 + idx - tt * cpb;
+        const bool in = idx < n * cpb;
+        rv[i] = (in && c < vdim) ? v[(size_t)(t0 + tt) * v_stride + (size_t)h * vdim + c] : from_f32<T>(0.f);
+        rb[i] = (in && b) ? b[(size_t)(t0 + tt) * ab_stride + h] : 1.f;
+      }
+    }
+    if (threadIdx.x < n) ra = a[(size_t)(t0 + threadIdx.x) * ab_stride + h];
+  };
+  if (PRE && beg < end) ask(beg, min(kScanChunk, end - beg));
+
   for (int t0 = beg; t0 < end; t0 += kScanChunk) {
     const int n = min(kScanChunk, end - t0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n * dpad; idx += kScanThreads) {
-      const int tt = idx / dpad, e = idx - tt * dpad;
-      const bool in = e < dim;
-      float qv = in ? to_f32(q[(size_t)(t0 + tt) * q_stride + (size_t)g * dim + e]) : 0.f;
-      float kv = in ? to_f32(k[(size_t)(t0 + tt) * k_stride + (size_t)g * dim + e]) : 0.f;
-      if (act) {
-        qv = qv / (1.0f + expf(-qv));
-        kv = kv / (1.0f + expf(-kv));
+    if (PRE) {
+#pragma unroll
+      for (int i = 0; i < NQ; ++i) {
+        const int idx = threadIdx.x + i * kScanThreads;
+        if (idx < n * dpad) {
+          float qv = to_f32(rq[i]), kv = to_f32(rk[i]);  // zero past dim
+          if (act) {
+            qv = qv / (1.0f + expf(-qv));
+            kv = kv / (1.0f + expf(-kv));
+          }
+          qs[idx] = qv * q_scale;
+          ksm[idx] = kv;
+        }
       }
-      qs[idx] = qv * q_scale;
-      ksm[idx] = kv;
+      if (threadIdx.x < n) as[threadIdx.x] = ra;
+    } else {
+      for (int idx = threadIdx.x; idx < n * dpad; idx += kScanThreads) {
+        const int tt = idx / dpad, e = idx - tt * dpad;
+        const bool in = e < dim;
+        float qv = in ? to_f32(q[(size_t)(t0 + tt) * q_stride + (size_t)g * dim + e]) : 0.f;
+        float kv = in ? to_f32(k[(size_t)(t0 + tt) * k_stride + (size_t)g * dim + e]) : 0.f;
+        if (act) {
+          qv = qv / (1.0f + expf(-qv));
+          kv = kv / (1.0f + expf(-kv));
+        }
+        qs[idx] = qv * q_scale;
+        ksm[idx] = kv;
+      }
+      if (threadIdx.x < n) as[threadIdx.x] = a[(size_t)(t0 + threadIdx.x) * ab_stride + h];
     }
-    for (int idx = threadIdx.x; idx < n * cpb; idx += kScanThreads) {
-      const int tt = idx / cpb, cc = idx - tt * cpb;
-      const int c = c0 + cc;
-      float vv = c < vdim ? to_f32(v[(size_t)(t0 + tt) * v_stride + (size_t)h * vdim + c]) : (c == vdim && ones_col ? 1.f : 0.f);
-      if (act && c < vdim) vv = vv / (1.0f + expf(-vv));
-      vs[idx] = b ? b[(size_t)(t0 + tt) * ab_stride + h] * vv : vv;
+    if (vpre) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int idx = threadIdx.x + i * kScanThreads;
+        if (idx < n * cpb) {
+          const int tt = idx / cpb, c = c0 + idx - tt * cpb;
+          float vv = c < vdim ? to_f32(rv[i]) : (c == vdim && ones_col ? 1.f : 0.f);
+          if (act && c < vdim) vv = vv / (1.0f + expf(-vv));
+          vs[idx] = rb[i] * vv;
+        }
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < n * cpb; idx += kScanThreads) {
+        const int tt = idx / cpb, cc = idx - tt * cpb;
+        const int c = c0 + cc;
+        float vv = c < vdim ? to_f32(v[(size_t)(t0 + tt) * v_stride + (size_t)h * vdim + c]) : (c == vdim && ones_col ? 1.f : 0.f);
+        if (act && c < vdim) vv = vv / (1.0f + expf(-vv));
+        vs[idx] = b ? b[(size_t)(t0 + tt) * ab_stride + h] * vv : vv;
+      }
     }
-    if (threadIdx.x < n) as[threadIdx.x] = a[(size_t)(t0 + threadIdx.x) * ab_stride + h];
     __syncthreads();
+    if (PRE && t0 + kScanChunk < end) ask(t0 + kScanChunk, min(kScanChunk, end - t0 - kScanChunk));
     for (int tt = 0; tt < n; ++tt) {
       const float at = as[tt];
       float bv[CPT], p[CPT];
@@ -177,6 +242,7 @@ ARLE_API int arle_decay_scan(const void* q, const void* k, const void* v, int dt
 #define ARLE_SCAN(TT, E) \
   return launch_scan<TT, E>(q, k, v, q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, R, H, \
                             kq_heads, dim, vdim, ones_col, q_scale, ab_stride, act, s)
+  // numbers of a column a lane holds: 4 up to 128 (eight at 128, with 16 lanes a column, measured 1.25 to 2 times slower)
   if (dtype == 0) {
     if (dim <= 128) ARLE_SCAN(float, 4);
     if (dim <= 256) ARLE_SCAN(float, 8);

@@ -78,8 +78,8 @@ class Attention(Mixer):
     def __init__(self, spec: AttentionSpec):
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if spec.head_dim % 2 or spec.head_dim > 256:
-            raise ValueError(f"head_dim {spec.head_dim} not supported (even, at most 256)")
+        if spec.head_dim > 256 or spec.head_dim <= 0:
+            raise ValueError(f"head_dim {spec.head_dim} not supported (at most 256)")
         if spec.window is not None and spec.window <= 0:
             raise ValueError("window must be positive")
         if spec.qk_norm not in ("head", "row", "head_after_rotation") or spec.values not in ("projected", "keys"):
@@ -94,7 +94,9 @@ class Attention(Mixer):
         self.spec = spec
         self.own_keys = spec.own_keys
         self.general_form = bool(spec.keep_first or spec.softcap is not None or spec.bias or spec.conv_taps
-                                 or (spec.qk_norm == "head" and self.vd != spec.head_dim))
+                                 or (spec.qk_norm == "head" and (self.vd != spec.head_dim or spec.head_dim % 2)))
+        if spec.head_dim % 2 and not self.general_form:
+            raise ValueError(f"head_dim {spec.head_dim} not supported by this form of attention (even sizes only)")
         if self.general_form and (spec.qk_norm != "head" or spec.values != "projected" or spec.head_gate or spec.sink is not None
                                   or not spec.own_keys or not spec.qk_norm_weight):
             raise ValueError("attention: kept first tokens, capped scores, biases and the convolution go with a per-head norm before "
@@ -274,7 +276,7 @@ class Attention(Mixer):
             proj = conv
         elif s.bias:
             ops.bias_add(proj, self.b_qkv)
-        if vd == hd:
+        if vd == hd and hd % 2 == 0:
             ops.attention_prep(proj, ctx.positions, cache.slot_mapping, self.q_norm, self.k_norm, s.qk_norm_eps or 0.0, inv_freq, rdim,
                                cache.k, cache.v, nq, nkv, hd, cache.page_size, angles=self._angles(proj, ctx, inv_freq, rdim))
         else:

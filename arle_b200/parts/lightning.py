@@ -8,7 +8,7 @@ No positions, no softmax, no cache that grows: what a request keeps is the heads
 slot that the cache manager zeroes when a request gets the slot.  The four input projections are one packed product;
 the silu of q, k and v is applied by the scan as it stages them; the recurrence is the package's scalar-decay scan with the
 decays as one number per head; the norm over all heads, its weight and the gate are one kernel.  ``decay`` are the heads'
-constants (each in (0, 1]); nothing else scales q.
+constants (usually in (0, 1]); nothing else scales q.
 """
 from __future__ import annotations
 
@@ -44,8 +44,8 @@ class ConstantDecayAttention(Mixer):
     def __init__(self, spec: ConstantDecayAttentionSpec):
         if min(spec.num_heads, spec.key_dim, spec.value_dim) <= 0 or spec.key_dim > 512:
             raise ValueError("constant-decay attention: heads, key_dim (at most 512) and value_dim must be positive")
-        if len(spec.decay) != spec.num_heads or not all(0.0 < float(d) <= 1.0 for d in spec.decay):
-            raise ValueError(f"constant-decay attention: one decay in (0, 1] per head, got {len(spec.decay)} for {spec.num_heads} heads")
+        if len(spec.decay) != spec.num_heads or not all(0.0 <= float(d) < float("inf") for d in spec.decay):
+            raise ValueError(f"constant-decay attention: one decay (not negative) per head, got {len(spec.decay)} for {spec.num_heads} heads")
         if spec.activation not in ("silu", "none"):
             raise ValueError(f"constant-decay attention: activation {spec.activation!r} (silu, none)")
         self.spec = spec

@@ -81,7 +81,8 @@ def test_model_spec_shares_latents_keeps_first_pages_and_packs_two_states():
     (lambda c: c["layers"][0]["mixer"].update(heads=3), "heads"),
     (lambda c: c["layers"][1]["mixer"].pop("q_rank"), "q_rank"),
     (lambda c: c["layers"][3]["mixer"]["right"].update(decay=[0.5, 0.5]), "decay"),
-    (lambda c: c["layers"][3]["mixer"]["right"].update(decay=[0.5, 0.5, 1.5]), "decay"),
+    (lambda c: c["layers"][3]["mixer"]["right"].update(decay=[0.5, 0.5, -0.1]), "decay"),
+    (lambda c: c["layers"][0]["mixer"].update(softcap=-2.0), "softcap"),
     (lambda c: c["layers"][3]["mixer"]["left"].update(softcap=0.0), "softcap"),
     (lambda c: c["layers"][3]["mixer"].pop("left"), "left"),
     (lambda c: c["layers"][0].update(mlp={"kind": "dense", "ff": 8}), "mlp"),

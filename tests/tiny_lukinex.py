@@ -78,7 +78,7 @@ TINY_K2 = model(157, 48, 2e-6, [
     layer(latent(5, 4, 6, 36, 8, 0.5), None),
     layer(parallel(left(2, 1, 20, 28, 0.2, window=5, keep_first=11, rot_dims=4, conv=5, softcap=2.0, factor=1.5), right(5, 4, 6, (0.3, 0.5, 0.8, 0.95, 1.0))),
           None),
-    layer(attn(6, 2, 8, 4, 0.5, window=1000, keep_first=4), moe(8, 5, 12, 1.0)),
+    layer(attn(6, 2, 9, 4, 0.5, window=1000, keep_first=4, rot_dims=6, factor=3.3), moe(8, 5, 12, 1.0)),      # an odd head size
     layer(latent(1, 24, 16, 36, 40, 0.2, kv_from=2), moe(2, 2, 20, 3.0, shared=(32, 1.0))),
     layer(parallel(left(3, 1, 16, 16, 0.25, conv=2), right(2, 12, 20, (0.97, 0.7))), moe(4, 2, 28, 1.1))])
 # K3: wider: heads of 64 and 128 with values as wide as keys, a latent of 128, aligned rows
