@@ -22,12 +22,16 @@
 // takes them).  The key range of a row is [max(0, kv_len - window), kv_len).
 // With keep_first > 0 the keys below keep_first that the window has passed are visible too: they stand in front of the
 // window's keys as whole tiles (the last one padded with masked places), so that no tile holds keys of both runs and the
-// splits cut the joined run.  With a cap, a score s (after the scale) becomes cap * tanh(s / cap) (tanhf).
+// splits cut the joined run.  With a cap, a score s (after the scale) becomes cap * tanh(s / cap) (tanh as 1 - 2 / (1 + e^(2x))).
 #include "common.cuh"
 #include "mma_utils.cuh"
 using namespace arle;
 
 namespace {
+
+// tanh(x) = 1 - 2 / (1 + e^(2x)): two special-function instructions, absolute error about 1e-7 (times the cap: far below
+// what rounding P to bfloat16 costs); exact at both ends (e^(2x) = 0 and infinity).
+__device__ __forceinline__ float tanh_by_exp(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
 
 constexpr int kThreads = 128;
 constexpr int kTile = 64;   // keys per tile
@@ -177,7 +181,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
         const int kj = kbeg + 8 * n + 2 * tq;
         if (cap_log2 > 0.f) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) s[n][e] = cap_log2 * tanhf(s[n][e] * scale_over_cap);
+          for (int e = 0; e < 4; ++e) s[n][e] = cap_log2 * tanh_by_exp(s[n][e] * scale_over_cap);
         } else {
 #pragma unroll
           for (int e = 0; e < 4; ++e) s[n][e] *= scale_log2;

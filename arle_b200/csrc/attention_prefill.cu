@@ -16,12 +16,16 @@
 // skip_single is set (the decode kernel takes them).
 // With keep_first > 0 a windowed query also sees the keys below keep_first: the tiles that hold them (counted from key 0)
 // run before the window's tiles, under the same mask.  With a cap, a score s (after the scale) becomes cap * tanh(s / cap)
-// before the softmax (tanhf, not the approximate instruction: the cap multiplies its error).
+// before the softmax (tanh as 1 - 2 / (1 + e^(2x)), not the approximate tanh instruction, whose error the cap would multiply).
 #include "common.cuh"
 #include "mma_utils.cuh"
 using namespace arle;
 
 namespace {
+
+// tanh(x) = 1 - 2 / (1 + e^(2x)): two special-function instructions, absolute error about 1e-7 (times the cap: far below
+// what rounding P to bfloat16 costs); exact at both ends (e^(2x) = 0 and infinity).
+__device__ __forceinline__ float tanh_by_exp(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
 
 constexpr int kThreads = 128;
 constexpr int kBlockM = 64;
@@ -180,7 +184,7 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
         const int kj = k0 + 8 * n + 2 * tq;
         if (cap_log2 > 0.f) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) s[n][e] = cap_log2 * tanhf(s[n][e] * scale_over_cap);
+          for (int e = 0; e < 4; ++e) s[n][e] = cap_log2 * tanh_by_exp(s[n][e] * scale_over_cap);
         } else {
 #pragma unroll
           for (int e = 0; e < 4; ++e) s[n][e] *= scale_log2;

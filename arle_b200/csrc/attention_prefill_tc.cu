@@ -16,7 +16,8 @@
 //   warps 0-3, 4-7   : softmax and epilogue of tile A and of tile B; thread i owns query row i
 //                      (TMEM lane i), so row maxima and sums need no shuffles.  A thread reads
 //                      its row of S into registers, masks (key <= query position, and >
-//                      position - window) and finds the row maximum; O and the running sum are
+//                      position - window; with kept first keys also every key below keep_first, whose tiles run
+//                      in front of the window's; with a cap the score becomes cap * tanh(score / cap)) and finds the row maximum; O and the running sum are
 //                      rescaled only when the maximum grew by more than 2^8 since the last
 //                      rescale (the exponentials stay within float32 and bfloat16 range); then
 //                      it exponentiates, adds up and writes P into tensor memory (tcgen05.st),
@@ -85,6 +86,9 @@ __device__ __forceinline__ float ex2_fast(float x) {          // 2^x on the spec
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// tanh(x) = 1 - 2 / (1 + e^(2x)): two special-function instructions, absolute error about 1e-7; exact at both ends.
+__device__ __forceinline__ float tanh_by_exp(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -126,8 +130,10 @@ struct Block {
   int r, h, kvh, t0, mbeg;
   int rows_x[2], pf_x[2], pl_x[2], jlo_x[2], jhi_x[2];
   int kb, ntiles, lo, p_last;
+  int nk, keep;      // key tiles of kept first keys in front of the window's tiles (tile j < nk starts at key j * BKV), and how many keys are kept
   // false: the block is beyond the request's queries (or the request is one that the decode kernel serves)
-  __device__ bool init(int b, int nq, int nkv, int nyb, const int* q_indptr, const int* kv_lens, int window, int skip_single) {
+  __device__ bool init(int b, int nq, int nkv, int nyb, const int* q_indptr, const int* kv_lens, int window, int skip_single,
+                       int keep_first) {
     h = b % nq;
     const int y = (b / nq) % nyb;
     r = b / (nq * nyb);
@@ -152,10 +158,14 @@ struct Block {
       lo_x[x] = (window > 0 && pf_x[x] - window + 1 > 0) ? pf_x[x] - window + 1 : 0;
     }
     kb = lo_x[0] / BKV * BKV;
+    // Kept first keys (a windowed query sees the keys below keep_first too): the tiles that hold those before kb run first.
+    // When kept keys reach into the window's tiles, a query tile starts at the window's first tile whatever its own first key.
+    keep = window > 0 ? keep_first : 0;
+    nk = (min(keep, kb) + BKV - 1) / BKV;
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
-      jlo_x[x] = (lo_x[x] / BKV * BKV - kb) / BKV;
-      jhi_x[x] = rows_x[x] > 0 ? (pl_x[x] - kb) / BKV + 1 : 0;
+      jlo_x[x] = nk + (keep > kb ? 0 : (lo_x[x] / BKV * BKV - kb) / BKV);
+      jhi_x[x] = rows_x[x] > 0 ? nk + (pl_x[x] - kb) / BKV + 1 : 0;
       if (rows_x[x] == 0) jlo_x[x] = 0;
     }
     ntiles = max(jhi_x[0], jhi_x[1]);
@@ -163,18 +173,27 @@ struct Block {
     p_last = rows_x[1] > 0 ? pl_x[1] : pl_x[0];        // last key any row of the block sees
     return true;
   }
-  __device__ bool in_range(int x, int j) const { return j >= jlo_x[x] && j < jhi_x[x]; }
+  // E: the form with kept first keys (the usual form compiles to what it was without them: nk is zero there)
+  template <bool E> __device__ bool in_range(int x, int j) const {
+    return E ? (j >= jlo_x[x] || j < nk) && j < jhi_x[x] : j >= jlo_x[x] && j < jhi_x[x];
+  }
+  template <bool E> __device__ int tile_key(int j) const { return (E && j < nk) ? j * BKV : kb + (j - (E ? nk : 0)) * BKV; }      // first key of tile j
 };
 
 constexpr int kWorkReaders = 11;             // who reads a drawn ticket: the two loader warps, the MMA thread, eight softmax warps
 
+// EXT: with kept first keys and a score cap (the usual form compiles without either).
+template <bool EXT>
 __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, const int* __restrict__ q_indptr,
     const int* __restrict__ kv_lens, const int* __restrict__ block_table, int bt_stride, int bt_width, int nq, int nkv,
-    int page_size, float scale_log2, float sink_log2, int window, int skip_single, int nyb, int nblocks, int ticket_slot, int* __restrict__ err) {
+    int page_size, float scale_log2, float sink_log2, int window, int skip_single, int nyb, int nblocks, int ticket_slot, int* __restrict__ err,
+    int keep_arg, float cap_arg, float scale_over_cap) {
   pdl_launch_dependents();
   pdl_wait();
+  const int keep_first = EXT ? keep_arg : 0;
+  const float cap_log2 = EXT ? cap_arg : 0.f;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = base;                              // 2 x TILE
@@ -191,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   // the CTA's first block is the one of its own index: its shape is worked out while the rest is set up
   bool first_has_queries = false;
   if (warp == kKeyWarp && lane == 0)
-    first_has_queries = work_blk[0].init((int)blockIdx.x, nq, nkv, nyb, q_indptr, kv_lens, window, skip_single);
+    first_has_queries = work_blk[0].init((int)blockIdx.x, nq, nkv, nyb, q_indptr, kv_lens, window, skip_single, keep_first);
   if (threadIdx.x == 0) {
     mbar_init(smem_addr(&q_full), 1);
     mbar_init(smem_addr(&q_empty), 1);
@@ -259,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
             if (!*aborted) {
               const unsigned int tk = draw_ticket(nblocks, ticket_slot);
               if (tk < (unsigned int)nblocks) b = (int)tk; else ended = true;
-              if (b >= 0 && !work_blk[it & 1].init(b, nq, nkv, nyb, q_indptr, kv_lens, window, skip_single)) b = -2;
+              if (b >= 0 && !work_blk[it & 1].init(b, nq, nkv, nyb, q_indptr, kv_lens, window, skip_single, keep_first)) b = -2;
             }
           } else {
             abort_flag = 1;
@@ -293,15 +312,20 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
         const int* bt = block_table + (size_t)blk.r * bt_stride;
         // Page ids come 32 at a time, one per lane, with the next 32 already in flight, so that no
         // tile waits for a read of the block table; a lane picks its page with a shuffle.
-        int p0 = blk.kb / page_size;
+        int p0 = blk.template tile_key<EXT>(0) / page_size;
         int cur = __ldg(bt + min(p0 + lane, bt_width - 1));
         int nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
         bool stop = false;
         for (int j = 0; j < blk.ntiles; ++j) {
           const int st = issued % kStages;
           const uint32_t par = (uint32_t)((issued / kStages) & 1);
-          const int key0 = blk.kb + j * BKV + c * 16;
-          while ((blk.kb + j * BKV) / page_size - p0 >= 32) {
+          const int key0 = blk.template tile_key<EXT>(j) + c * 16;
+          if (EXT && blk.template tile_key<EXT>(j) / page_size - p0 >= 64) {          // from the kept tiles on to the window's: start again there
+            p0 = blk.template tile_key<EXT>(j) / page_size;
+            cur = __ldg(bt + min(p0 + lane, bt_width - 1));
+            nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
+          }
+          while (blk.template tile_key<EXT>(j) / page_size - p0 >= 32) {
             cur = nxt;
             p0 += 32;
             nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
@@ -310,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
           const int rel = pi - p0;                                // 0 .. 63: a tile spans at most 8 pages
           const int from_cur = __shfl_sync(0xffffffffu, cur, rel & 31), from_nxt = __shfl_sync(0xffffffffu, nxt, rel & 31);
           int row = -1;
-          if (lane < 16 && key0 <= blk.p_last && key0 + 15 >= blk.lo) {
+          if (lane < 16 && key0 <= blk.p_last && (EXT ? (key0 < blk.keep || (j >= blk.nk && key0 + 15 >= blk.lo)) : key0 + 15 >= blk.lo)) {
             const int page = rel < 32 ? from_cur : from_nxt;
             row = (page * nkv + blk.kvh) * page_size + (key0 - pi * page_size);
           }
@@ -384,8 +408,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
           ok = mbar_wait_bounded(smem_addr(&k_full[g0 % kStages]), (uint32_t)((g0 / kStages) & 1), aborted);
           if (ok) {
             tc_fence_after();
-            if (blk.in_range(0, 0)) issue_s(0, 0);
-            if (blk.in_range(1, 0)) issue_s(1, 0);
+            if (blk.template in_range<EXT>(0, 0)) issue_s(0, 0);
+            if (blk.template in_range<EXT>(1, 0)) issue_s(1, 0);
             umma_commit(smem_addr(&k_empty[g0 % kStages]));
             if (blk.ntiles == 1) umma_commit(smem_addr(&q_empty));        // every S of the block is issued
           }
@@ -396,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
           bool v_ready = false, k_ready = false;
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
-            if (blk.in_range(x, j)) {
+            if (blk.template in_range<EXT>(x, j)) {
               if (!mbar_wait_bounded(smem_addr(&p_full[x]), (uint32_t)(done_p[x] & 1), aborted)) { ok = false; break; }
               if (!v_ready) {
                 if (!mbar_wait_bounded(smem_addr(&v_full[vst]), (uint32_t)(((g0 + j) / kStages) & 1), aborted)) { ok = false; break; }
@@ -421,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
               }
             }
             // S of the next key tile goes over this P: the tensor core runs them in the order issued
-            if (blk.in_range(x, j + 1)) {
+            if (blk.template in_range<EXT>(x, j + 1)) {
               if (!k_ready) {
                 if (!mbar_wait_bounded(smem_addr(&k_full[knext]), (uint32_t)(((g0 + j + 1) / kStages) & 1), aborted)) { ok = false; break; }
                 k_ready = true;
@@ -463,13 +487,15 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       const int p_first = blk.pf_x[x], pl = blk.pl_x[x];
       const int jlo = blk.jlo_x[x], jhi = blk.jhi_x[x], rows_here = blk.rows_x[x];
       const int kb = blk.kb;
+      const int keep = EXT ? blk.keep : 0, nk = EXT ? blk.nk : 0;      // without kept keys both are zero when the kernel is compiled
       const int p_row = min(p_first + row, pl);
       const int lo_row = window > 0 ? p_row - window + 1 : 0;
       float m_used = -INFINITY, l = 0.f;
       int n = 0;
-      for (int j = jlo; j < jhi; ++j, ++n, ++n_all) {
-        const int k0 = kb + j * BKV;
-        const bool full_tile = k0 + BKV - 1 <= p_first && (window <= 0 || k0 >= pl - window + 1);
+      for (int j = (EXT && rows_here > 0 && nk > 0) ? 0 : jlo; j < jhi; ++j) {
+        if (EXT && j >= nk && j < jlo) continue;               // between the kept tiles and this query tile's first
+        const int k0 = (EXT && j < nk) ? j * BKV : kb + (j - nk) * BKV;
+        const bool full_tile = (EXT && j < nk) ? k0 + BKV <= keep : (k0 + BKV - 1 <= p_first && (window <= 0 || k0 >= pl - window + 1));
         bool ready = mbar_wait_bounded(smem_addr(&s_full[x]), (uint32_t)(n_all & 1), aborted);
         if (__any_sync(0xffffffffu, !ready)) { ok = false; break; }
         tc_fence_after();
@@ -488,6 +514,15 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
             for (int c = 0; c < 4; ++c)
 #pragma unroll
               for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[c][i]));
+          } else if (EXT && k0 < keep) {                      // a tile with kept first keys: those stay whatever the window says
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int kj = k0 + c * 32 + i;
+                if (!(kj <= p_row && (kj >= lo_row || kj < keep))) sv[c][i] = 0xff800000u;
+                m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[c][i]));
+              }
           } else {
 #pragma unroll
             for (int c = 0; c < 4; ++c)
@@ -498,7 +533,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
                 m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[c][i]));
               }
           }
-          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+          // the cap grows with the score, so the capped maximum is the cap of the maximum (a row without keys stays at -inf)
+          mx = (EXT && cap_log2 > 0.f) ? (mx == -INFINITY ? mx : cap_log2 * tanh_by_exp(mx * scale_over_cap)) : mx * scale_log2;
         }
         const float m_new = fmaxf(m_used, mx);
         const bool grow = m_new > m_used + kRescaleStep;        // also true when the row sees its first key
@@ -530,8 +567,15 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
           for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float e0 = ex2_fast(fmaf(__uint_as_float(sv[2 * h2 + c][i]), scale_log2, -m_eff));
-              const float e1 = ex2_fast(fmaf(__uint_as_float(sv[2 * h2 + c][i + 1]), scale_log2, -m_eff));
+              float e0, e1;
+              if (EXT && cap_log2 > 0.f) {                      // a masked score stays masked: tanh(-inf) is -1, not -inf
+                const float s0 = __uint_as_float(sv[2 * h2 + c][i]), s1 = __uint_as_float(sv[2 * h2 + c][i + 1]);
+                e0 = s0 == -INFINITY ? 0.f : ex2_fast(fmaf(cap_log2, tanh_by_exp(s0 * scale_over_cap), -m_eff));
+                e1 = s1 == -INFINITY ? 0.f : ex2_fast(fmaf(cap_log2, tanh_by_exp(s1 * scale_over_cap), -m_eff));
+              } else {
+                e0 = ex2_fast(fmaf(__uint_as_float(sv[2 * h2 + c][i]), scale_log2, -m_eff));
+                e1 = ex2_fast(fmaf(__uint_as_float(sv[2 * h2 + c][i + 1]), scale_log2, -m_eff));
+              }
               l4[(i >> 1) & 3] += e0 + e1;
               packed[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
             }
@@ -542,6 +586,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_addr(&p_full[x]));
+        ++n;
+        ++n_all;
       }
       if (ok && n > 0) {
         const bool ready = mbar_wait_bounded(smem_addr(&o_full[x]), (uint32_t)(o_all & 1), aborted);
@@ -598,7 +644,7 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
                                              const void* v_cache, long long cache_pages, const int* q_indptr,
                                              const int* kv_lens, const int* block_table, int bt_stride, int bt_width, int nq, int nkv,
                                              int hd, int page_size, float scale, float sink, int window, int rows, int max_q_len,
-                                             int skip_single, int* err, cudaStream_t s) {
+                                             int skip_single, int* err, int keep_first, float softcap, cudaStream_t s) {
   if (rows <= 0 || max_q_len <= 0) return 0;
   if (bt_width < 1) return ARLE_E_BADARG;
   if (hd != HD || page_size % 16 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || rows > 65535 || (max_q_len + BQ2 - 1) / BQ2 > 65535)
@@ -614,11 +660,14 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
   rc = tensor_map_2d_bf16(v_cache, cache_rows, HD, HD, 16, &mv);
   if (rc) return rc;
   const size_t smem = (2 + 2 * kStages) * (size_t)TILE + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (keep_first < 0 || softcap < 0.f) return ARLE_E_BADARG;
+  const bool ext = (window > 0 && keep_first > 0) || softcap > 0.f;
+  auto kernel = ext ? paged_prefill_tc_kernel<true> : paged_prefill_tc_kernel<false>;
+  static bool configured[2] = {false, false};
+  if (!configured[ext]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[ext] = true;
   }
   // CTAs stay resident and draw blocks (a query head, 256 queries of a request) from a counter, the heaviest first
   const int nyb = (max_q_len + BQ2 - 1) / BQ2;
@@ -630,9 +679,11 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
   const int ctas = (int)(nblocks < sms ? nblocks : sms);
   static unsigned int launches = 0;
   const int ticket_slot = (int)(launches++ % kTicketSlots);
-  cudaError_t e = launch_kernel(paged_prefill_tc_kernel, dim3(ctas), dim3(kThreads), smem, s, 1, mq, mk, mv, (__nv_bfloat16*)out,
+  cudaError_t e = launch_kernel(kernel, dim3(ctas), dim3(kThreads), smem, s, 1, mq, mk, mv, (__nv_bfloat16*)out,
                                 q_indptr, kv_lens, block_table, bt_stride, bt_width, nq, nkv, page_size,
-                                scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, skip_single, nyb, (int)nblocks, ticket_slot, err);
+                                scale * 1.4426950408889634f, sink * 1.4426950408889634f, window, skip_single, nyb, (int)nblocks, ticket_slot, err,
+                                window > 0 ? keep_first : 0, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f,
+                                softcap > 0.f ? scale / softcap : 0.f);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }

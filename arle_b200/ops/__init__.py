@@ -74,7 +74,7 @@ _SIGNATURES = {
     "arle_decode_stream_plan": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _I, _F, _P],
     "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I,
-                                        _I, _I, _I, _P, _P],
+                                        _I, _I, _I, _P, _I, _F, _P],
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "arle_gemm_plain_bf16": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "arle_gemm_skinny": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -559,16 +559,12 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
         raise KernelError("paged_attention: block table rows must be contiguous")
     keep_first = int(keep_first or 0) if window else 0
     if batch is not None and _KERNEL_SET == "fast" and vd == hd and fast_attention_supported(q, nq, nkv, hd):
-        # kept first keys and capped scores are in the mma.sync prompt kernel and the split-KV decode kernel
+        # kept first keys and capped scores are in both prompt kernels and in the split-KV decode kernel (not the streaming one)
         extended = bool(keep_first or softcap)
-        if batch.max_q_len > 1 and extended:
-            paged_attention_prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                                    window, batch.max_q_len, skip_single=batch.num_single > 0, sink=sink, keep_first=keep_first,
-                                    softcap=softcap)
-        elif batch.max_q_len > 1:
+        if batch.max_q_len > 1:
             prefill = paged_attention_prefill_tc if tc_attention_supported(q, hd, page_size) else paged_attention_prefill
             prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                    window, batch.max_q_len, skip_single=batch.num_single > 0, sink=sink)
+                    window, batch.max_q_len, skip_single=batch.num_single > 0, sink=sink, keep_first=keep_first, softcap=softcap)
         if batch.num_single > 0 and not extended and stream_decode_supported(batch.num_rows, page_size, nq // nkv):
             ctas = sm_count(q.device)
             slots = (ctas + batch.num_rows * nkv) * (nq // nkv)
@@ -617,7 +613,8 @@ def tc_attention_supported(q, hd: int, page_size: int) -> bool:
 
 
 def paged_attention_prefill_tc(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                               window, max_q_len: int, skip_single: bool = False, sink: float = None) -> None:
+                               window, max_q_len: int, skip_single: bool = False, sink: float = None, keep_first: int = 0,
+                               softcap: float = None) -> None:
     """Flash attention over the paged cache on the tcgen05 tensor cores (TMA-fed, scores
     and output in tensor memory) for rows with several queries."""
     R = kv_lens.numel()
@@ -627,8 +624,8 @@ def paged_attention_prefill_tc(q, out, k_cache, v_cache, q_indptr, kv_lens, bloc
     _check(library().arle_paged_attention_prefill_tc(
         _ptr(q), q.stride(0), q.shape[0], _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(q_indptr),
         _ptr(kv_lens), _ptr(block_table), block_table.stride(0), block_table.shape[1], nq, nkv, hd, page_size, float(scale),
-        _sink_arg(sink), int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _ptr(error_flag(q.device)), _stream()),
-        "paged_attention_prefill_tc")
+        _sink_arg(sink), int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _ptr(error_flag(q.device)),
+        int(keep_first or 0), float(softcap or 0.0), _stream()), "paged_attention_prefill_tc")
 
 
 _SM_COUNT: dict = {}

@@ -216,9 +216,11 @@ def test_routing_by_a_softmax_over_the_chosen():
 
 @pytest.mark.parametrize("cap", [None, 3.0])
 @pytest.mark.parametrize("nq,nkv,hd,ps,window,keep", [(8, 2, 128, 16, 37, 20), (4, 1, 64, 16, 33, 5), (2, 2, 64, 32, 300, 100), (12, 4, 128, 8, 64, 64),
-                                                       (4, 4, 64, 16, 40, 0), (4, 2, 128, 16, None, 7)])
+                                                       (4, 4, 64, 16, 40, 0), (4, 2, 128, 16, None, 7), (2, 1, 128, 32, 100, 290), (4, 2, 128, 16, 150, 129),
+                                                       (2, 2, 128, 16, 20, 600)])
 def test_kept_first_keys_and_capped_scores_in_the_tensor_core_attention_kernels(nq, nkv, hd, ps, window, keep, cap):
-    """Prompts on mma.sync and decoding with split keys (one split and several), with requests shorter than what is kept,
+    """Prompts on mma.sync and on tcgen05 (kept keys over one, two and several of its 128-key tiles, reaching into the window's
+    first tile, and beyond a whole short request) and decoding with split keys (one split and several), with requests shorter than what is kept,
     shorter than the window, and far longer than both: each against the plain statement, which differs from the attention
     without the kept keys, and from the one without the cap, by far more than the tolerance.  The pages that no query can
     see hold poison."""
@@ -250,10 +252,11 @@ def test_kept_first_keys_and_capped_scores_in_the_tensor_core_attention_kernels(
         assert (exp - want(q, kc, vc, pos, rows, bt, 0, cap)).abs().max() > 0.05
     if cap:
         assert (exp - want(q, kc, vc, pos, rows, bt, keep, None)).abs().max() > 0.05
-    out = torch.zeros(q.shape[0], nq * hd, dtype=torch.bfloat16, device=DEV)
-    ops.paged_attention_prefill(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, scale, window, max(q_lens), keep_first=keep, softcap=cap)
-    ops.check_errors(DEV)
-    torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+    for fn in ([ops.paged_attention_prefill_tc] if hd == 128 and ps % 16 == 0 else []) + [ops.paged_attention_prefill]:
+        out = torch.zeros(q.shape[0], nq * hd, dtype=torch.bfloat16, device=DEV)
+        fn(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, scale, window, max(q_lens), keep_first=keep, softcap=cap)
+        ops.check_errors(DEV)
+        torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
     lens = [1, 63, 64, 65, 700, 2049, 17, keep + 1, (window or 50) + keep]
     R = len(lens)
     q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, [1] * R, seed=3)
