@@ -31,7 +31,9 @@ using namespace arle;
 constexpr int kScanChunk = 16;
 constexpr int kScanThreads = 256;
 
-template <typename T, int EPL, int CPT>
+// AHEAD: the variant that asks for the next chunk while this one's steps run (steps of prompt portions; it holds more registers,
+// which a step of decoded tokens, bound by reading and writing the memories, pays for in blocks per SM).
+template <typename T, int EPL, int CPT, bool AHEAD>
 __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int q_stride, int k_stride, int v_stride,
     const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ state, long slot_stride,
@@ -64,8 +66,9 @@ __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
   // holds at most NQ numbers of q and of k (16 tokens x 32 lanes x EPL / 256 threads) and NV of v.
   constexpr int NQ = 2 * EPL;
   constexpr int NV = 2;
-  constexpr bool PRE = EPL <= 8;
-  const bool vpre = PRE && kScanChunk * cpb <= NV * kScanThreads;
+  constexpr bool PRE = AHEAD;
+  const bool pre = PRE && end - beg > kScanChunk;       // a row of one chunk (a decoded token) has nothing to ask for ahead
+  const bool vpre = pre && kScanChunk * cpb <= NV * kScanThreads;
   const int dshift = __ffs(dpad) - 1;                    // dpad is a power of two
   T rq[PRE ? NQ : 1], rk[PRE ? NQ : 1], rv[NV];
   float rb[NV], ra = 0.f;
@@ -90,12 +93,12 @@ __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
     }
     if (threadIdx.x < n) ra = a[(size_t)(t0 + threadIdx.x) * ab_stride + h];
   };
-  if (PRE && beg < end) ask(beg, min(kScanChunk, end - beg));
+  if (pre) ask(beg, kScanChunk);
 
   for (int t0 = beg; t0 < end; t0 += kScanChunk) {
     const int n = min(kScanChunk, end - t0);
     __syncthreads();
-    if (PRE) {
+    if (pre) {
 #pragma unroll
       for (int i = 0; i < NQ; ++i) {
         const int idx = threadIdx.x + i * kScanThreads;
@@ -146,7 +149,7 @@ __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
       }
     }
     __syncthreads();
-    if (PRE && t0 + kScanChunk < end) ask(t0 + kScanChunk, min(kScanChunk, end - t0 - kScanChunk));
+    if (pre && t0 + kScanChunk < end) ask(t0 + kScanChunk, min(kScanChunk, end - t0 - kScanChunk));
     for (int tt = 0; tt < n; ++tt) {
       const float at = as[tt];
       float bv[CPT], p[CPT];
@@ -194,17 +197,20 @@ __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
 template <typename T, int EPL, int CPT>
 static int launch_scan_as(const void* q, const void* k, const void* v, int q_stride, int k_stride, int v_stride, const float* a,
                           const float* b, float* state, long slot_stride, const int* q_indptr, const int* state_slots, float* out,
-                          int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, int lpc, int ab_stride, int act, cudaStream_t s) {
+                          int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, int lpc, int ab_stride, int act, bool ahead,
+                          cudaStream_t s) {
   const int cpb = kScanThreads / lpc * CPT;
   const int vcols = vdim + ones_col;
   const size_t smem = ((size_t)2 * kScanChunk * lpc * EPL + (size_t)kScanChunk * cpb + kScanChunk) * sizeof(float);
   if (smem > 200 * 1024) return ARLE_E_UNSUPPORTED;
+  // four numbers a lane (columns of up to 128) gain from asking ahead; eight a lane were measured slower with it
+  auto kernel = (ahead && EPL == 4) ? decay_scan_kernel<T, EPL, CPT, EPL == 4> : decay_scan_kernel<T, EPL, CPT, false>;
   if (smem > 40 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<T, EPL, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((vcols + cpb - 1) / cpb, H, R);
-  launch_kernel(decay_scan_kernel<T, EPL, CPT>, dim3(grid), dim3(kScanThreads), smem, s, 1, (const T*)q, (const T*)k, (const T*)v,
+  launch_kernel(kernel, dim3(grid), dim3(kScanThreads), smem, s, 1, (const T*)q, (const T*)k, (const T*)v,
                 q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, H, kq_heads, dim, vdim, ones_col,
                 q_scale, lpc, ab_stride, act);
   return launch_status();
@@ -215,33 +221,34 @@ static int launch_scan_as(const void* q, const void* k, const void* v, int q_str
 template <typename T, int EPL>
 static int launch_scan(const void* q, const void* k, const void* v, int q_stride, int k_stride, int v_stride, const float* a,
                        const float* b, float* state, long slot_stride, const int* q_indptr, const int* state_slots, float* out,
-                       int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, int ab_stride, int act, cudaStream_t s) {
+                       int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, int ab_stride, int act, bool ahead, cudaStream_t s) {
   int lpc = 1;
   while (lpc * EPL < dim) lpc <<= 1;
   const int wide = kScanThreads / lpc * 4;
   const long blocks_wide = (long)((vdim + ones_col + wide - 1) / wide) * H * R;
   if (blocks_wide >= 148)
     return launch_scan_as<T, EPL, 4>(q, k, v, q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, R, H,
-                                     kq_heads, dim, vdim, ones_col, q_scale, lpc, ab_stride, act, s);
+                                     kq_heads, dim, vdim, ones_col, q_scale, lpc, ab_stride, act, ahead, s);
   return launch_scan_as<T, EPL, 1>(q, k, v, q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, R, H,
-                                   kq_heads, dim, vdim, ones_col, q_scale, lpc, ab_stride, act, s);
+                                   kq_heads, dim, vdim, ones_col, q_scale, lpc, ab_stride, act, ahead, s);
 }
 
 // q, k [T, kq_heads*dim] and v [T, H*vdim] in the activation type (row strides given); a, b float32 [T, H] (ab_stride = H), or
 // one number a head for all tokens (ab_stride = 0: a float32 [H], b float32 [H] or null for ones: a memory with a constant
-// decay per head); act 1: silu on q, k and v as they are staged; state: float32,
+// decay per head); act 1: silu on q, k and v as they are staged; long_rows: the step's rows are mostly longer than a chunk of
+// 16 tokens (a hint: the variant that asks for the next chunk ahead is launched); state: float32,
 // a slot every slot_stride numbers, [H][vdim + ones_col][dim] at its start; out float32 [T, H, vdim + ones_col].
 ARLE_API int arle_decay_scan(const void* q, const void* k, const void* v, int dtype, int q_stride, int k_stride, int v_stride,
                              const float* a, const float* b, float* state, long slot_stride, const int* q_indptr,
                              const int* state_slots, float* out, int R, int H, int kq_heads, int dim, int vdim, int ones_col,
-                             float q_scale, int ab_stride, int act, cudaStream_t s) {
+                             float q_scale, int ab_stride, int act, int long_rows, cudaStream_t s) {
   if (R <= 0) return 0;
   if (!a || (ab_stride != 0 && ab_stride != H) || (act != 0 && act != 1)) return ARLE_E_BADARG;
   if (H <= 0 || kq_heads <= 0 || H % kq_heads || dim <= 0 || vdim <= 0 || H > 65535 || R > 65535) return ARLE_E_BADARG;
   if (dim > 32 * 16) return ARLE_E_UNSUPPORTED;
 #define ARLE_SCAN(TT, E) \
   return launch_scan<TT, E>(q, k, v, q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, R, H, \
-                            kq_heads, dim, vdim, ones_col, q_scale, ab_stride, act, s)
+                            kq_heads, dim, vdim, ones_col, q_scale, ab_stride, act, long_rows != 0, s)
   // numbers of a column a lane holds: 4 up to 128 (eight at 128, with 16 lanes a column, measured 1.25 to 2 times slower)
   if (dtype == 0) {
     if (dim <= 128) ARLE_SCAN(float, 4);

@@ -91,7 +91,7 @@ _SIGNATURES = {
     "arle_latent_prep": [_P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_latent_attention": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-    "arle_decay_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "arle_decay_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_mlstm_gates": [_P, _I, _P, _P, _F, _P, _P, _P, ctypes.c_long, ctypes.c_long, _P, _P, _P, _I, _I, _P],
     "arle_mlstm_out": [_P, _P, _P, _I, _I, _P, _F, _P, _I, _I, _I, _I, _P],
     "arle_ssm_gates": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
@@ -1218,7 +1218,8 @@ def decay_scan(q, k, v, a, b, state, q_indptr, state_slots, out, heads: int, kq_
         raise KernelError("decay_scan: q_indptr must have one entry more than state_slots")
     _check(library().arle_decay_scan(_ptr(q), _ptr(k), _ptr(v), _dt(q), q.stride(0), k.stride(0), v.stride(0), _ptr(a), _ptr(b),
                                      _ptr(state), state.stride(0), _ptr(q_indptr), _ptr(state_slots), _ptr(out), R, heads, kq_heads,
-                                     dim, vdim, vcols - vdim, float(q_scale), 0 if per_head else heads, int(act == "silu"), _stream()),
+                                     dim, vdim, vcols - vdim, float(q_scale), 0 if per_head else heads, int(act == "silu"), int(T > 16 * R),
+                                     _stream()),
            "decay_scan")
 
 
