@@ -86,6 +86,11 @@ __device__ __forceinline__ float ex2_fast(float x) {          // 2^x on the spec
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float rcp_fast(float x) {          // 1 / x on the special-function unit; infinity gives 0
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // tanh(x) = 1 - 2 / (1 + e^(2x)): two special-function instructions, absolute error about 1e-7; exact at both ends.
 __device__ __forceinline__ float tanh_by_exp(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
 
@@ -194,6 +199,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   pdl_wait();
   const int keep_first = EXT ? keep_arg : 0;
   const float cap_log2 = EXT ? cap_arg : 0.f;
+  const float cap_c1 = scale_over_cap * 2.8853900817779268f, cap_c2 = -2.0f * cap_log2;      // e^(2z) as a power of two; -2 cap
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = base;                              // 2 x TILE
@@ -568,10 +574,13 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
               float e0, e1;
-              if (EXT && cap_log2 > 0.f) {                      // a masked score stays masked: tanh(-inf) is -1, not -inf
+              if (EXT && cap_log2 > 0.f) {
+                // 2^(cap tanh(z) - m) with tanh(z) = 1 - 2 / (1 + e^(2z)): t = e^(2z), r = 1 / (1 + t), 2^((cap - m) - 2 cap r): a
+                // chain of six instructions a score.  A masked score stays masked: tanh(-inf) is -1, not -inf.
                 const float s0 = __uint_as_float(sv[2 * h2 + c][i]), s1 = __uint_as_float(sv[2 * h2 + c][i + 1]);
-                e0 = s0 == -INFINITY ? 0.f : ex2_fast(fmaf(cap_log2, tanh_by_exp(s0 * scale_over_cap), -m_eff));
-                e1 = s1 == -INFINITY ? 0.f : ex2_fast(fmaf(cap_log2, tanh_by_exp(s1 * scale_over_cap), -m_eff));
+                const float r0 = rcp_fast(1.0f + ex2_fast(s0 * cap_c1)), r1 = rcp_fast(1.0f + ex2_fast(s1 * cap_c1));
+                e0 = s0 == -INFINITY ? 0.f : ex2_fast(fmaf(r0, cap_c2, cap_log2 - m_eff));
+                e1 = s1 == -INFINITY ? 0.f : ex2_fast(fmaf(r1, cap_c2, cap_log2 - m_eff));
               } else {
                 e0 = ex2_fast(fmaf(__uint_as_float(sv[2 * h2 + c][i]), scale_log2, -m_eff));
                 e1 = ex2_fast(fmaf(__uint_as_float(sv[2 * h2 + c][i + 1]), scale_log2, -m_eff));
